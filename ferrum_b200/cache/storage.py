@@ -1,12 +1,14 @@
 """Device memory of the cache, laid out for the groups the model's layers form.
 
 `CacheLayout` reads a model's schedule: runs whose mixers keep paged keys/values with the
-same (kv heads, head size, window) form a group; each writing run gets a plane of its own in
-the group's pool, a run with `cache_of` shares the plane of the run it names.  Runs whose
-mixers keep a fixed-size state get a state array [max_requests, ...] indexed by slot id.
+same (kv heads, head size, window, parts) form a group; each writing run gets a plane of its own in
+the group's pool, a run with `cache_of` shares the plane of the run it names (it may look back
+over another window: the plane then keeps what the widest of its readers needs).  Runs whose
+mixers (or blocks) keep a fixed-size state get a state array [max_requests, ...] indexed by slot
+id; a state always belongs to one run, also when the run reads another run's pages.
 
-`CacheStorage` allocates one pool per group, [planes, pages, 2 (K, V), kv heads, page_size,
-head size] in the compute dtype, the state arrays, and the native `CacheManager` that owns
+`CacheStorage` allocates one pool per group, [planes, pages, parts (K, V; or one), kv heads,
+page_size, head size] in the compute dtype, the state arrays, and the native `CacheManager` that owns
 the page and slot numbers.  Page size and page counts are parameters (the pool is sized for
 the tokens the caller wants resident, or for a fraction of the free HBM).
 """
@@ -41,18 +43,26 @@ class CacheLayout:
         self.run_plane: List[Optional[int]] = []
         self.run_state: List[Optional[int]] = []
         self.state_needs = []
+        # the window a writing run's plane must keep: the widest of the runs that read it (0: everything)
+        keep = {k: [need.paged.window] for k, (run, need) in enumerate(zip(self.schedule, self.needs))
+                if run.cache_of is None and need.paged is not None}
         for k, (run, need) in enumerate(zip(self.schedule, self.needs)):
             if run.cache_of is not None:
                 j = run.cache_of
-                if (need.paged is None) != (self.needs[j].paged is None) or (
-                        need.paged is not None and need.paged != self.needs[j].paged):
+                a, b = need.paged, self.needs[j].paged
+                if (a is None) != (b is None) or (a is not None and (a.n_kv_heads, a.head_dim, a.parts) !=
+                                                  (b.n_kv_heads, b.head_dim, b.parts)):
                     raise ValueError(f"run {k} cannot read the cache of run {j}: their needs differ")
+                if a is not None:
+                    keep[j].append(a.window)
+        for k, (run, need) in enumerate(zip(self.schedule, self.needs)):
+            if run.cache_of is not None:
+                j = run.cache_of
                 self.run_group.append(self.run_group[j])
                 self.run_plane.append(self.run_plane[j])
-                self.run_state.append(self.run_state[j])
-                continue
-            if need.paged is not None:
-                key = (need.paged.n_kv_heads, need.paged.head_dim, need.paged.window)
+            elif need.paged is not None:
+                window = 0 if min(keep[k]) <= 0 else max(keep[k])
+                key = (need.paged.n_kv_heads, need.paged.head_dim, window, need.paged.parts)
                 if key not in self.group_keys:
                     self.group_keys.append(key)
                     self.group_planes.append(0)
@@ -71,7 +81,7 @@ class CacheLayout:
 
     def bytes_per_token(self, dtype) -> int:
         size = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * h * d * planes * size for (h, d, _), planes in zip(self.group_keys, self.group_planes))
+        return sum(parts * h * d * planes * size for (h, d, _, parts), planes in zip(self.group_keys, self.group_planes))
 
 
 class CacheStorage:
@@ -99,8 +109,8 @@ class CacheStorage:
         self.manager = host.module().CacheManager(specs, int(max_requests))
         self.max_requests = int(max_requests)
         self.pools = []
-        for g, (hkv, d, _w) in enumerate(self.layout.group_keys):
-            self.pools.append(torch.empty((self.layout.group_planes[g], pages[g], 2, hkv, self.page_size, d),
+        for g, (hkv, d, _w, parts) in enumerate(self.layout.group_keys):
+            self.pools.append(torch.empty((self.layout.group_planes[g], pages[g], parts, hkv, self.page_size, d),
                                           dtype=dtype, device=device))
         self.states = [torch.zeros((self.max_requests,) + tuple(n.shape), dtype=n.dtype, device=device)
                        for n in self.layout.state_needs]

@@ -192,8 +192,11 @@ def cmd_bench(opts):
         with open(path) as f:
             cfgd = json.load(f)
         if "--layers" in opts:
-            cfgd["num_hidden_layers"] = opts["--layers"]
-        arch = registry.lookup(cfgd["architectures"][0])
+            if isinstance(cfgd.get("layers"), list):       # a config that lists its layers one by one
+                cfgd["layers"] = cfgd["layers"][:opts["--layers"]]
+            else:
+                cfgd["num_hidden_layers"] = opts["--layers"]
+        arch = registry.lookup(registry.architecture_name(cfgd, path))
         model = arch.build(arch.read_config(cfgd), parse_dtype(dtype), "cuda", max_positions=max_len)
         init_random(model, opts.get("--seed", 0))
     else:

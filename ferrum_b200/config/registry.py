@@ -67,12 +67,23 @@ def read_config(folder_or_file: str):
             d = json.load(f)
     except (OSError, ValueError) as e:
         raise ConfigError(f"cannot read {path}: {e}") from None
-    if not isinstance(d, dict) or not d.get("architectures"):
-        raise ConfigError(f"{path}: no 'architectures' entry")
-    arch = lookup(str(d["architectures"][0]))
+    arch = lookup(architecture_name(d, path))
     return arch, arch.read_config(d)
+
+
+def architecture_name(d, path="config.json"):
+    """The name a config.json files its model under: the first of `architectures`, or the
+    string `architecture`."""
+    if isinstance(d, dict):
+        if d.get("architectures"):
+            return str(d["architectures"][0])
+        if isinstance(d.get("architecture"), str) and d["architecture"]:
+            return d["architecture"]
+    raise ConfigError(f"{path}: no 'architectures' entry")
 
 
 def _ensure_builtin():
     if "LlamaForCausalLM" not in _REGISTRY:
         from ..models import llama  # noqa: F401  (registers itself)
+    if "Ruperax" not in _REGISTRY:
+        from ..models import ruperax  # noqa: F401

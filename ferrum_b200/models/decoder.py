@@ -57,8 +57,13 @@ class DecoderModel(Part):
         return {name: (spec, part, local) for name, spec, part, local in self.named_specs()}
 
     def cache_needs(self):
-        """One CacheNeed per schedule entry (what that run's mixer keeps per request)."""
-        return [self.blocks[r.block].mixer.cache_need() for r in self.schedule]
+        """One CacheNeed per schedule entry: what that run's mixer keeps per request, or what its
+        block says it keeps (a block with a state of its own has a `cache_need`)."""
+        out = []
+        for r in self.schedule:
+            b = self.blocks[r.block]
+            out.append(b.cache_need() if hasattr(b, "cache_need") else b.mixer.cache_need())
+        return out
 
     @property
     def n_vocab(self):

@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 7
+ABI = 8
 
 
 def lib():
@@ -198,13 +198,24 @@ def dtype_code(dtype):
 
 
 # ----------------------------------------------------------------------------- ops
-def embedding(table, ids, out, err):
-    """out[t] = table[ids[t]] as float32."""
+def embedding(table, ids, out, err, scale=1.0, pos_table=None, positions=None):
+    """out[t] = table[ids[t]] as float32; with `scale` the row is multiplied by it, with `pos_table`
+    ([positions, E], the table's dtype) row positions[t] of it is added."""
     _need(table, None, "table", 2); _need(ids, torch.int32, "ids", 1); _need(out, torch.float32, "out", 2)
     V, E = table.shape
     T = ids.shape[0]
     if out.shape[0] < T or out.shape[1] != E or not table.is_contiguous() or not out.is_contiguous():
         raise KernelError("embedding: out must be contiguous [>=T, E] and table contiguous")
+    if scale != 1.0 or pos_table is not None:
+        if pos_table is not None:
+            _need(pos_table, table.dtype, "pos_table", 2); _need(positions, torch.int32, "positions", 1)
+            if pos_table.shape[1] != E or not pos_table.is_contiguous() or positions.shape[0] < T:
+                raise KernelError("embedding: pos_table must be contiguous [positions, E]")
+        _check(lib().ferrum_embedding_scaled(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), c_int(T), c_int(E),
+                                             c_int(V), c_float(scale), _ptr(pos_table), _ptr(positions),
+                                             c_int(pos_table.shape[0] if pos_table is not None else 0), _ptr(err),
+                                             _stream()), "embedding_scaled")
+        return
     _check(lib().ferrum_embedding(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), c_int(T), c_int(E),
                                   c_int(V), _ptr(err), _stream()), "embedding")
 
@@ -218,10 +229,11 @@ class Partials:
         self._c = (c_int * 4)(*layout)
 
 
-def rmsnorm(x, weight, out, eps, rows=None, n_rows=None, partials=None):
+def rmsnorm(x, weight, out, eps, rows=None, n_rows=None, partials=None, groups=1):
     """out[r] = rmsnorm(x[rows[r] if rows else r]) * weight; x float32, out float32 or bfloat16.
     With `partials` (a deferred residual product) the rows of x first get the partials added,
-    in place."""
+    in place.  groups > 1: the row is cut into that many equal consecutive parts and each is
+    divided by its own root mean square."""
     _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1); _need(out, None, "out", 2)
     E = x.shape[1]
     if n_rows is None:
@@ -230,6 +242,12 @@ def rmsnorm(x, weight, out, eps, rows=None, n_rows=None, partials=None):
         raise KernelError("rmsnorm: shapes do not agree")
     if rows is not None:
         _need(rows, torch.int32, "rows", 1)
+    if groups != 1:
+        if partials is not None:
+            raise KernelError("rmsnorm: a grouped norm takes no pending product")
+        _check(lib().ferrum_group_norm(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows), c_int(n_rows),
+                                       c_int(E), c_int(groups), c_float(eps), _stream()), "group_norm")
+        return
     if partials is not None:
         _check(lib().ferrum_rmsnorm_reduce(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows),
                                            c_int(n_rows), c_int(E), c_float(eps), _ptr(partials.workspace), partials._c,
@@ -471,3 +489,104 @@ def sample(logits, n_rows, out_ids, err, inv_temperature=None, seeds=None, count
     _check(lib().ferrum_sample(_ptr(logits), c_int(logits.stride(0)), c_int(n_rows), c_int(logits.shape[1]),
                                _ptr(inv_temperature), _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(also_to),
                                _ptr(err), _stream()), "sample")
+
+
+# ----------------------------------------------------------------------------- parallel gated block
+def norm_pair_shift(x, w1, w2, shift, a, m, b, n_tokens, ctx, state, stage, groups, eps):
+    """Both norms of a parallel block and the token shift of the mixer's input (gated_block.cu):
+    a = n * w1, b = n * w2 (b, w2 may be None), m = a + (previous a - a) * shift (shift None: m = a).
+    `ctx` gives positions, req_of_token, q_start and slots; state [slots, E] and stage [requests, E]
+    are float32."""
+    _need(x, torch.float32, "x", 2); _need(w1, torch.float32, "w1", 1); _need(a, None, "a", 2); _need(m, a.dtype, "m", 2)
+    E = x.shape[1]
+    if not (x.is_contiguous() and a.is_contiguous() and m.is_contiguous()) or a.shape[1] != E or m.shape[1] != E:
+        raise KernelError("norm_pair_shift: rows must be contiguous [T, E]")
+    if b is not None:
+        _need(b, a.dtype, "b", 2); _need(w2, torch.float32, "w2", 1)
+    if shift is not None:
+        _need(shift, torch.float32, "shift", 1); _need(state, torch.float32, "state", 2); _need(stage, torch.float32, "stage", 2)
+        if state.shape[1] != E or stage.shape[1] != E or stage.shape[0] < ctx.n_reqs or not state.is_contiguous():
+            raise KernelError("norm_pair_shift: state and stage rows must have E elements")
+    _check(lib().ferrum_norm_pair_shift(_ptr(x), _ptr(w1), _ptr(w2), _ptr(shift), _ptr(a), _ptr(m), _ptr(b), dtype_code(a.dtype),
+                                        c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.req_of_token), _ptr(ctx.q_start),
+                                        _ptr(ctx.slots), _ptr(state), _ptr(stage), c_int(E), c_int(groups), c_float(eps),
+                                        _stream()), "norm_pair_shift")
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def bias_glu(gu, bias_gate, bias_up, act, n_tokens, F, kind="silu"):
+    """act[t, f] = f(gu[t, f] + bias_gate[f]) * (gu[t, F + f] + bias_up[f]); gu float32."""
+    _need(gu, torch.float32, "gu", 2); _need(act, None, "act", 2)
+    for bias in (bias_gate, bias_up):
+        if bias is not None:
+            _need(bias, torch.float32, "bias", 1)
+    _check(lib().ferrum_bias_glu(_ptr(gu), c_int(gu.stride(0)), _ptr(bias_gate), _ptr(bias_up), _ptr(act), dtype_code(act.dtype),
+                                 c_int(act.stride(0)), c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), _stream()), "bias_glu")
+
+
+def gated_residual(x, n_tokens, y1, g1, c1, y2=None, c2=None, g2=None, c3=None, ctx=None, stage=None, state=None):
+    """x += y1 * sigmoid(g1 + c1) + (y2 + c2) * sigmoid(g2 + c3), all float32 (the second term only with
+    y2).  With `state` the staged row of every request whose portion ends in this batch is copied
+    into its state row."""
+    _need(x, torch.float32, "x", 2)
+    for t in (y1, g1, y2, g2):
+        if t is not None:
+            _need(t, torch.float32, "operand", 2)
+    ld = lambda t: c_int(t.stride(0) if t is not None else 0)
+    _check(lib().ferrum_gated_residual(_ptr(x), c_int(n_tokens), c_int(x.shape[1]), _ptr(y1), ld(y1), _ptr(g1), ld(g1), _ptr(c1),
+                                       _ptr(y2), ld(y2), _ptr(c2), _ptr(g2), ld(g2), _ptr(c3),
+                                       _ptr(ctx.req_of_token if state is not None else None),
+                                       _ptr(ctx.q_start if state is not None else None),
+                                       _ptr(ctx.slots if state is not None else None), _ptr(stage), _ptr(state), _stream()),
+           "gated_residual")
+
+
+# ----------------------------------------------------------------------------- attention over a cached latent
+def latent_prep(proj, n_tokens, off_q, q_rank, wq, off_kv, kv_rank, rot_dim, wkv, off_gate, n_gate, ctx, block_table, rot,
+                plane, page_stride, page_size, cq, gate, eps):
+    """From a token's float32 down-projections: the normalised query latent `cq`, the cache row
+    (normalised latent, rotated key part) at the token's page (off_kv < 0: no cache write) and the
+    sigmoid of the gate logits (latent.cu)."""
+    _need(proj, torch.float32, "proj", 2); _need(cq, None, "cq", 2); _need(gate, torch.float32, "gate", 2)
+    if off_kv >= 0:
+        _need(plane, cq.dtype, "plane")
+    cos_sin = rot.cos_sin if rot is not None else None
+    _check(lib().ferrum_latent_prep(_ptr(proj), c_int(proj.stride(0)), c_int(n_tokens), c_int(off_q), c_int(q_rank), _ptr(wq),
+                                    c_int(off_kv), c_int(kv_rank), c_int(rot_dim), _ptr(wkv), c_int(off_gate), c_int(n_gate),
+                                    _ptr(ctx.positions), _ptr(ctx.req_of_token), _ptr(block_table), c_int(block_table.shape[1]),
+                                    _ptr(cos_sin), c_int(cos_sin.shape[0] if rot is not None else 0),
+                                    c_int(rot.rope_dim if rot is not None else 0), _ptr(plane if off_kv >= 0 else None),
+                                    c_longlong(page_stride), c_int(page_size), _ptr(cq), c_int(cq.stride(0)),
+                                    dtype_code(cq.dtype), _ptr(gate), c_float(eps), _ptr(ctx.err), _stream()), "latent_prep")
+
+
+def latent_q_rope(q, qf, n_tokens, positions, rot, H, Dn, Rr, R, err):
+    """The rotated part of every query head (q: heads of Dn + Rr) into qf (heads of R + Rr) at R."""
+    _need(q, None, "q", 2); _need(qf, q.dtype, "qf", 2)
+    cos_sin = rot.cos_sin if rot is not None else None
+    _check(lib().ferrum_latent_q_rope(_ptr(q), c_int(q.stride(0)), _ptr(qf), c_int(qf.stride(0)), dtype_code(q.dtype),
+                                      c_int(n_tokens), _ptr(positions), _ptr(cos_sin),
+                                      c_int(cos_sin.shape[0] if rot is not None else 0),
+                                      c_int(rot.rope_dim if rot is not None else 0), c_int(H), c_int(Dn), c_int(Rr), c_int(R),
+                                      _ptr(err), _stream()), "latent_q_rope")
+
+
+def attention_latent(qf, out, gate, n_tokens, ctx, block_table, plane, page_stride, page_size, H, Dk, Dv, scale, window,
+                     single_tokens):
+    """Attention of every token over its request's cached rows of Dk elements, whose first Dv
+    elements are the values; qf: heads of Dk, out: heads of Dv, times gate[t, h] (latent.cu)."""
+    _need(qf, None, "qf", 2); _need(out, qf.dtype, "out", 2); _need(plane, qf.dtype, "plane")
+    if gate is not None:
+        _need(gate, torch.float32, "gate", 2)
+    global _work
+    if _profile is not None:
+        keys = sum(min(p + n, window + n) if window > 0 else p + n for p, n in zip(ctx.h_pos0, ctx.h_q_len))
+        pairs = sum(n * (min(p + n, window) if window > 0 else p + (n + 1) / 2) for p, n in zip(ctx.h_pos0, ctx.h_q_len))
+        _work = (keys * Dk * plane.element_size() + n_tokens * H * (Dk + Dv) * qf.element_size(), 2.0 * pairs * H * (Dk + Dv))
+    _check(lib().ferrum_attention_latent(_ptr(qf), c_int(qf.stride(0)), _ptr(out), c_int(out.stride(0)), dtype_code(qf.dtype),
+                                         _ptr(gate), c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.q_start), c_int(ctx.n_reqs),
+                                         _ptr(block_table), c_int(block_table.shape[1]), _ptr(plane), c_longlong(page_stride),
+                                         c_int(page_size), c_int(H), c_int(Dk), c_int(Dv), c_float(scale), c_int(window),
+                                         c_int(1 if single_tokens else 0), _ptr(ctx.err), _stream()), "attention_latent")

@@ -1,12 +1,13 @@
 from .attention import PagedAttention
 from .base import (CacheNeed, FeedForward, Mixer, Norm, PagedKVNeed, ParamSpec, Part, PositionEncoding,
                    StateNeed)
-from .block import PreNormBlock
-from .embedding import OutputHead, TokenEmbedding
+from .block import ParallelGatedBlock, PreNormBlock
+from .embedding import LearnedPositions, OutputHead, TokenEmbedding
+from .latent_attention import LatentAttention
 from .ffn import SwiGLU
 from .norm import RMSNorm
 from .rope import RotaryEmbedding
 
 __all__ = ["PagedAttention", "CacheNeed", "FeedForward", "Mixer", "Norm", "PagedKVNeed", "ParamSpec", "Part",
-           "PositionEncoding", "StateNeed", "PreNormBlock", "OutputHead", "TokenEmbedding", "SwiGLU", "RMSNorm",
+           "PositionEncoding", "StateNeed", "PreNormBlock", "ParallelGatedBlock", "LatentAttention", "LearnedPositions", "OutputHead", "TokenEmbedding", "SwiGLU", "RMSNorm",
            "RotaryEmbedding"]

@@ -15,7 +15,7 @@ import torch
 from ..ops import lib as ops
 from . import attention_plan
 from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
-from .linear import RESIDUAL, STORE, linear, linear_deferred
+from .linear import RESIDUAL, STORE, STORE_F32, linear, linear_deferred
 
 
 # Up to this many tokens in a step the attention kernel lets the kernels after it start early
@@ -62,7 +62,7 @@ class PagedAttention(Mixer):
     def cache_need(self):
         return CacheNeed(paged=PagedKVNeed(self.Hkv, self.D, self.window))
 
-    def forward(self, x, ctx, cache, residual):
+    def forward(self, x, ctx, cache, residual, accumulate=True):
         T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
         qw = Hq * D
         qkv = ctx.buf("attn_qkv", (ctx.token_capacity, (Hq + 2 * Hkv) * D), self.dtype)
@@ -81,7 +81,7 @@ class PagedAttention(Mixer):
             self._flash(qkv, out, ctx, cache, table)
         else:
             self._generic(qkv, out, ctx, cache, table)
-        linear(out, self.w_output_weight, residual, RESIDUAL, ctx, M=T)
+        linear(out, self.w_output_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
 
     def _generic(self, qkv, out, ctx, cache, table):
         """CUDA-core path.  With enough rows to fill the GPU (a prompt portion) every row walks its

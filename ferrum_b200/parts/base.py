@@ -46,10 +46,13 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of `n_kv_heads` x `head_dim` per position; `window` 0 keeps all keys."""
+    """Keys and values of `n_kv_heads` x `head_dim` per position; `window` 0 keeps all keys.
+    `parts` 2: a page holds keys, then values; 1: one row per position and head (a mixer that
+    derives keys and values from the same cached row)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    parts: int = 2
 
 
 @dataclass(frozen=True)
@@ -125,10 +128,12 @@ class Mixer(Part):
         and while `ctx.fixed_shapes` is set make grid sizes depend on the batch's sizes only."""
         return None
 
-    def forward(self, x, ctx, cache, residual) -> None:
+    def forward(self, x, ctx, cache, residual, accumulate=True) -> None:
+        """accumulate=False: `residual` is a float32 buffer of the block's own that receives the
+        mixer's output instead of having it added (a block that scales it before the sum)."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, x, ctx, residual) -> None:
+    def forward(self, x, ctx, residual, accumulate=True) -> None:
         raise NotImplementedError

@@ -1,7 +1,8 @@
-"""Token embedding and output head.
+"""Token embedding, learned positions and output head.
 
 Embedding: row t of the table, upcast to the float32 residual stream, no scaling
-(crates/model/src/weights.rs:29-51).  Output head: logits = W_out x on the wanted rows only;
+(crates/model/src/weights.rs:29-51) unless a `scale` is given; a table of learned position
+vectors, when the model has one, is added by the same kernel (unscaled).  Output head: logits = W_out x on the wanted rows only;
 W_out is its own matrix or, when the file has none, the embedding table
 (crates/model/src/llama.rs:28-40,103-111).
 """
@@ -10,15 +11,17 @@ from __future__ import annotations
 import torch
 
 from ..ops import lib as ops
-from .base import ParamSpec, Part
+from .base import ParamSpec, Part, PositionEncoding
 from .linear import STORE_F32, linear
 
 
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, n_vocab, width):
-        self.n_vocab, self.width = n_vocab, width
+    def __init__(self, n_vocab, width, scale=1.0, positions: "LearnedPositions" = None):
+        """positions: a `LearnedPositions` part whose vector for a token's position is added to the
+        (scaled) embedding; the model lists it as its position encoding, which owns the table."""
+        self.n_vocab, self.width, self.scale, self.positions = n_vocab, width, float(scale), positions
         self.w_weight = None
 
     def param_specs(self):
@@ -26,8 +29,24 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx):
         h = ctx.buf("hidden", (ctx.token_capacity, self.width), torch.float32)
-        ops.embedding(self.w_weight, ctx.token_ids, h, ctx.err)
+        pos = self.positions.w_weight if self.positions is not None else None
+        ops.embedding(self.w_weight, ctx.token_ids, h, ctx.err, scale=self.scale, pos_table=pos,
+                      positions=ctx.positions if pos is not None else None)
         return h
+
+
+class LearnedPositions(PositionEncoding):
+    """One learned vector per position, added to the embedded token.  The sum happens inside the
+    embedding kernel (`TokenEmbedding(positions=...)`); a position past the table raises the step's
+    error flag."""
+    graph_safe = True
+
+    def __init__(self, n_positions, width):
+        self.n_positions, self.width = int(n_positions), width
+        self.w_weight = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.n_positions, self.width))}
 
 
 class OutputHead(Part):

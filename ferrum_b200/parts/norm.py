@@ -1,4 +1,6 @@
-"""RMSNorm: x * rsqrt(mean(x^2) + eps) * w (crates/kernels/src/scalar.rs:143-156)."""
+"""RMSNorm: x * rsqrt(mean(x^2) + eps) * w (crates/kernels/src/scalar.rs:143-156).  With
+`groups` > 1 the row is cut into that many equal consecutive parts, each divided by its own root
+mean square (the reference has one group)."""
 from __future__ import annotations
 
 from ..ops import lib as ops
@@ -8,8 +10,10 @@ from .base import Norm, ParamSpec
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, width: int, eps: float, out_dtype):
-        self.width, self.eps, self.out_dtype = width, float(eps), out_dtype
+    def __init__(self, width: int, eps: float, out_dtype, groups: int = 1):
+        if groups < 1 or width % groups:
+            raise ValueError(f"{groups} groups do not divide a width of {width}")
+        self.width, self.eps, self.out_dtype, self.groups = width, float(eps), out_dtype, int(groups)
         self.w_weight = None
 
     def param_specs(self):
@@ -20,5 +24,9 @@ class RMSNorm(Norm):
         n = n_rows if n_rows is not None else ctx.n_tokens
         cap = ctx.want_capacity if rows is not None else ctx.token_capacity
         out = ctx.buf(tag + ("_rows" if rows is not None else ""), (cap, self.width), self.out_dtype)
+        if self.groups > 1:
+            ctx.flush_residual()
+            ops.rmsnorm(h, self.w_weight, out, self.eps, rows=rows, n_rows=n, groups=self.groups)
+            return out
         ops.rmsnorm(h, self.w_weight, out, self.eps, rows=rows, n_rows=n, partials=ctx.take_pending_residual(h))
         return out

@@ -25,6 +25,7 @@ _DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.fl
 INITS = {
     "normal": lambda shape, g, device, std: torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std,
     "ones_normal": lambda shape, g, device, std: 1.0 + torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std,
+    "uniform": lambda shape, g, device, std: torch.rand(shape, generator=g, device=device, dtype=torch.float32),
     "zeros": lambda shape, g, device, std: torch.zeros(shape, device=device, dtype=torch.float32),
 }
 
@@ -57,7 +58,7 @@ def init_random(model, seed, device="cuda", std=0.02):
 def write_random_model(config_dict, folder, seed, dtype="float32", std=0.02, tie=None):
     """Write `folder/config.json` and `folder/model.safetensors` for the architecture that
     config_dict names; tensor names are the checkpoint's (HF) names."""
-    arch = registry.lookup(str(config_dict["architectures"][0]))
+    arch = registry.lookup(registry.architecture_name(config_dict))
     cfg = arch.read_config(config_dict)
     model = arch.build(cfg, _DT[dtype], "cpu", max_positions=1)
     back = {v: k for k, v in (arch.hf_names(cfg) if arch.hf_names else {}).items()}
@@ -85,7 +86,7 @@ def write_random_gguf(config_dict, path, seed, dtype="float16", std=0.02):
     Llama file does."""
     from .gguf_io import write_gguf
     store = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}[dtype]
-    arch = registry.lookup(str(config_dict["architectures"][0]))
+    arch = registry.lookup(registry.architecture_name(config_dict))
     cfg = arch.read_config(config_dict)
     model = arch.build(cfg, torch.float32, "cpu", max_positions=1)
     tied = getattr(cfg, "tie_word_embeddings", False)

@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--model llama31-8b|llama32-3b|llama2-7b] [--dtype bf16|fp16|fp32]
-                    [--workload decode|serve] [--layers L] [--batch B] [--context S] [--trials N]
+                    [--workload decode|serve|latent] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
 
 Prints ONE JSON line.
 
@@ -24,6 +24,11 @@ ids in from pinned host memory, sampled ids back to the host, every step.
 `value` is generated tokens per second over the whole run; the line also gives the time to the
 first token (median and 95th percentile), preemptions, and what a step that cannot be replayed
 from a CUDA graph costs the host.
+
+`--workload latent`: the Ruperax design (latent attention in parallel gated blocks) at layer
+sizes that resemble real models (`--size`), beside a Llama of equal size: prefill of a 2048-token
+prompt, decode at batch 8 with 2048 cached tokens, and per kernel its time, bytes, flops and fraction
+of the measured roofline.  `value` is the design's decode rate.
 
 Weights are random N(0, 0.02); token ids are uniform random from a seed.  No L2 flush is needed
 between steps: a step reads gigabytes of weights, far more than the 126 MB L2 holds.
@@ -170,7 +175,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--model", default="llama31-8b", choices=sorted(MODELS), help="layer sizes (random weights)")
     ap.add_argument("--dtype", default="bf16", choices=sorted(DTYPES), help="compute dtype; fp32 is the true 32-bit path")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent"])
+    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent: the layer sizes to compare at")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=None,
                     help="cached tokens per request of the headline point (default 8192 for llama31-8b, 4096 for "
@@ -189,6 +195,8 @@ def main():
         return 2
     if args.workload == "serve":
         return serve(args)
+    if args.workload == "latent":
+        return latent(args)
     return decode(args)
 
 
@@ -471,6 +479,141 @@ def serve(args):
         "clocks": clk.summary(), "serve": best, "warmup_run": runs[0], "gpu_launches": best["gpu_launches"],
         "e2e": {"value": best["generated_tok_s"], "unit": "tok/s", "note": "the workload itself runs through Engine.step()"},
     }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------- latent attention beside Llama
+# Layer sizes that resemble real models; the Llama beside each has the same width, heads, head size,
+# feed-forward width, layers and vocabulary (a quarter as many KV heads as heads).
+LATENT_SIZES = {
+    "2b": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, ff=5632),
+    "8b": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, ff=14336),
+}
+
+
+def latent_configs(size, layers, vocab=32000, window=4096, groups=8):
+    s = LATENT_SIZES[size]
+    mixer = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "kv_rank": s["kv_rank"],
+             "q_rank": s["q_rank"], "scale": (s["dim"] + s["rot_dim"]) ** -0.5, "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": s["rot_dim"]}}
+    ours = {"architecture": "Ruperax", "vocab": vocab, "width": s["width"], "max_positions": 4096, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6, "groups": groups},
+            "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": s["ff"]}}
+                       for _ in range(layers)]}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": s["width"], "num_hidden_layers": layers,
+             "num_attention_heads": s["heads"], "num_key_value_heads": max(1, s["heads"] // 4), "head_dim": 128,
+             "intermediate_size": s["ff"], "vocab_size": vocab, "rope_theta": 10000.0, "max_position_embeddings": 4096,
+             "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+    return ours, llama
+
+
+def latent(args):
+    """Prefill (one 2048-token prompt in one step) and decode (batch 8 at 2048 cached tokens) of the
+    Ruperax design at real layer sizes beside a Llama of equal size, random weights, and per kernel
+    the time of one such step with its bytes, flops and fraction of the measured roofline (from
+    a profiled pass that launches kernel by kernel)."""
+    import torch
+    from ferrum_b200.cache import CacheStorage
+    from ferrum_b200.config import registry
+    from ferrum_b200.engine import ModelRunner, StepEntry
+    from ferrum_b200.engine.api import parse_dtype
+    from ferrum_b200.ops import lib as ops
+    from ferrum_b200.weights import init_random
+
+    W, K, N_TRIALS = max(3, args.warmup), max(1, args.steps), max(1, args.trials)
+    L = args.layers or 4
+    B, ctx_len, T = args.batch, args.context or 2048, 2048
+    td = parse_dtype(DTYPES[args.dtype])
+    pk = peaks()
+    page = 16
+    max_len = max(ctx_len, T) + W + K + 64
+    gen = torch.Generator().manual_seed(0)
+    out = {}
+    with ClockSampler() as clk:
+        for name, cfgd in zip(("ruperax", "llama"), latent_configs(args.size, L)):
+            arch = registry.lookup(registry.architecture_name(cfgd))
+            cfg = arch.read_config(cfgd)
+            model = arch.build(cfg, td, "cuda", max_positions=max_len)
+            init_random(model, 0, "cuda")
+            cache = CacheStorage(model, td, "cuda", page_size=page, max_tokens=B * (max_len + page), max_requests=B,
+                                 max_model_len=max_len)
+            for p in cache.pools:
+                p.normal_(0.0, 0.5)
+            runner = ModelRunner(model, cache, max_batch_tokens=T, max_batch_requests=B)
+            mgr = cache.manager
+            ids = torch.empty(B, dtype=torch.int32, device="cuda")
+
+            def tokens(n):
+                return torch.randint(0, cfg.n_vocab, (n,), generator=gen).tolist()
+
+            def prefill_once():
+                slot = cache.open()
+                toks = tokens(T)
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+                runner.step([StepEntry(slot, 0, toks, [T - 1])], check=False)
+                ev1.record()
+                torch.cuda.synchronize()
+                cache.close(slot)
+                return ev0.elapsed_time(ev1)
+
+            def decode_run(steps, warm):
+                slots = [cache.open() for _ in range(B)]
+                first = ctx_len - warm
+                for s in slots:
+                    mgr.grow(s, first - 1)
+                    mgr.commit(s, first - 1)
+                l0 = 0
+                for i in range(warm + steps):
+                    if i == warm:
+                        torch.cuda.synchronize()
+                        l0 = ops.launches
+                        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        ev0.record()
+                    entries = [StepEntry(s, first - 1 + i, [t], [0]) for s, t in zip(slots, tokens(B))]
+                    ops.sample(runner.step(entries, check=False), B, ids, runner.ctx.err)
+                ev1.record()
+                torch.cuda.synchronize()
+                n = ops.launches - l0
+                for s in slots:
+                    cache.close(s)
+                return ev0.elapsed_time(ev1) / steps, n
+
+            pre = [prefill_once() for _ in range(W + N_TRIALS)][W:]
+            dec = [decode_run(K, W) for _ in range(N_TRIALS)]
+            runner.check_device_errors()
+            # per kernel: one prompt step and four decode steps launched kernel by kernel
+            runner.use_graphs = False
+            kernels = {}
+            for what, fn in (("prefill", prefill_once), ("decode", lambda: decode_run(4, 1))):
+                fn()
+                ops.profile_begin()
+                fn()
+                rows = ops.profile_report(pk)
+                steps = 1 if what == "prefill" else 5
+                kernels[what] = [{"kernel": r["kernel"], "launches_per_step": round(r["launches"] / steps, 1),
+                                  "us_per_step": round(r["ms"] * 1e3 / steps, 1), "GBps": r.get("GBps"), "TFLOPs": r.get("TFLOPs"),
+                                  "frac": r.get("frac_of_roofline")} for r in rows]
+            ms_p, ms_d = statistics.median(pre), statistics.median([d[0] for d in dec])
+            out[name] = {"prefill_tok_s": round(T / ms_p * 1e3, 1), "prefill_ms": round(ms_p, 3),
+                         "decode_tok_s": round(B / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d, 4),
+                         "decode_launches_per_step": dec[0][1] // K, "kernels": kernels,
+                         "cache_bytes_per_token": CacheStorage.bytes_per_token_of(model, td)}
+            del runner, cache, model
+            gc.collect()
+            torch.cuda.empty_cache()
+    ours = out["ruperax"]
+    line = {"metric": f"decode tok/s (Ruperax {args.size} layer sizes, {args.dtype}, batch {B}, context {ctx_len})",
+            "value": ours["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": ours["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic", "impl": "ours",
+            "config": dict(LATENT_SIZES[args.size], model=f"Ruperax, {args.size} layer sizes, random weights", layers=L,
+                           global_batch=B, seq_len=ctx_len, prefill_tokens=T, window=4096, vocab=32000, page_size=page,
+                           parallelism="single GPU", l2="weights of a step exceed the L2 at these sizes"),
+            "clocks": clk.summary(), "gpu_launches": int(ours["decode_launches_per_step"] * K), "peaks": pk,
+            "ruperax": ours, "llama_equal_size": out["llama"]}
     print(json.dumps(line))
     return 0
 

@@ -175,6 +175,7 @@ __device__ __forceinline__ float4 lat_load4(const T* row, int d, int D, bool vec
 }
 
 constexpr int LAT_WARPS = 8;
+constexpr int LAT_SPLIT = 128;      // keys per split of a single token's key range
 
 struct LatSmem {
   int DK8, KS, off_q, off_p, off_row, bytes;
@@ -196,7 +197,7 @@ attention_latent_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
                         const int* __restrict__ positions, const int* __restrict__ q_start, int n_reqs,
                         const int* __restrict__ block_table, int table_width, const T* __restrict__ plane, long long page_stride,
                         int page_size, int H, int Dk, int Dv, float scale, int window, int* __restrict__ err, int vec, int TK,
-                        int DK8, int off_q, int off_p, int off_row) {
+                        int DK8, int off_q, int off_p, int off_row, float* __restrict__ part, int split_slots) {
   constexpr int TW = LAT_WARPS / HW, TQ = TH * TW;
   extern __shared__ __align__(16) float lat_sm[];
   const int KS = DK8 + 4;
@@ -240,6 +241,14 @@ attention_latent_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
       k_begin = min(k_begin, window > 0 ? max(0, p - window + 1) : 0);
       k_end = max(k_end, p + 1);
     }
+  }
+  if (part != nullptr) {
+    // (one token per CTA) the token's keys are cut at multiples of LAT_SPLIT in absolute positions:
+    // where a cut falls depends on the position alone, never on the batch
+    const int s = k_begin / LAT_SPLIT + blockIdx.y;
+    if (s * LAT_SPLIT >= k_end) return;
+    k_begin = max(k_begin, s * LAT_SPLIT);
+    k_end = min(k_end, (s + 1) * LAT_SPLIT);
   }
   int pos[TH], lo[TH];
 #pragma unroll
@@ -388,6 +397,19 @@ attention_latent_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
   for (int i = 0; i < TH; ++i) {
     if (i0 + i >= nt) break;
     const int t = t0 + i0 + i;
+    if (part != nullptr) {
+      float* p = part + (((size_t)t * H + h) * split_slots + blockIdx.y) * (Dv + 2);
+      if (lane == 0) {
+        p[0] = m[i];
+        p[1] = l[i];
+      }
+#pragma unroll
+      for (int e = 0; e < DVI; ++e) {
+        const int d = lane + 32 * e;
+        if (d < Dv) p[2 + d] = acc[i][e];
+      }
+      continue;
+    }
     const float f = (l[i] > 0.f ? 1.0f / l[i] : 0.f) * (gate != nullptr ? gate[(size_t)t * H + h] : 1.0f);
 #pragma unroll
     for (int e = 0; e < DVI; ++e) {
@@ -396,6 +418,45 @@ attention_latent_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
     }
   }
 }
+
+// Folds the splits of every (token, head) in ascending key order and applies the gate: one warp each.
+template <typename T>
+__global__ void __launch_bounds__(32)
+attention_latent_combine_kernel(T* __restrict__ out, int ldo, const float* __restrict__ part, const float* __restrict__ gate,
+                                const int* __restrict__ positions, int H, int Dv, int window, int split_slots) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+  const int pos = positions[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int n = min(pos / LAT_SPLIT - lo / LAT_SPLIT + 1, split_slots);
+  const float* base = part + ((size_t)t * H + h) * split_slots * (Dv + 2);
+  float M = -INFINITY, L = 0.f, O[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) O[i] = 0.f;
+  for (int s = 0; s < n; ++s) {
+    const float* p = base + (size_t)s * (Dv + 2);
+    const float mb = p[0], lb = p[1];
+    const float m_new = fmaxf(M, mb);
+    const float fa = M == -INFINITY ? 0.f : expf(M - m_new);
+    const float fb = mb == -INFINITY ? 0.f : expf(mb - m_new);
+    L = L * fa + lb * fb;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int d = lane + 32 * i;
+      if (d < Dv) O[i] = O[i] * fa + p[2 + d] * fb;
+    }
+    M = m_new;
+  }
+  const float f = (L > 0.f ? 1.0f / L : 0.f) * (gate != nullptr ? gate[(size_t)t * H + h] : 1.0f);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int d = lane + 32 * i;
+    if (d < Dv) out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<T>(O[i] * f);
+  }
+}
+
+FERRUM_API int ferrum_attention_latent_split() { return LAT_SPLIT; }
 
 constexpr int LAT_MAX_DK = 1024, LAT_MAX_DV = 512, LAT_SMEM_LIMIT = 200 * 1024;
 
@@ -406,7 +467,10 @@ constexpr int LAT_MAX_DK = 1024, LAT_MAX_DV = 512, LAT_SMEM_LIMIT = 200 * 1024;
 FERRUM_API int ferrum_attention_latent(const void* q, int ldq, void* out, int ldo, int dtype, const float* gate, int n_tokens,
                                        const int* positions, const int* q_start, int n_reqs, const int* block_table,
                                        int table_width, const void* plane, long long page_stride, int page_size, int H, int Dk,
-                                       int Dv, float scale, int window, int single_tokens, int* err_flag, cudaStream_t stream) {
+                                       int Dv, float scale, int window, int single_tokens, float* part, int split_slots,
+                                       int* err_flag, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(part == nullptr || (single_tokens && split_slots > 0 && split_slots <= 65535),
+                   "latent attention: key splits are for steps of single tokens (slots %d)", split_slots);
   FERRUM_CHECK_ARG(n_tokens >= 0 && n_reqs > 0 && H > 0, "latent attention: bad sizes T=%d requests=%d H=%d", n_tokens, n_reqs, H);
   FERRUM_CHECK_ARG(Dk > 0 && Dk <= LAT_MAX_DK && Dv > 0 && Dv <= Dk && Dv <= LAT_MAX_DV,
                    "latent attention: key size %d (at most %d) or value size %d (at most %d and the key size)", Dk, LAT_MAX_DK, Dv, LAT_MAX_DV);
@@ -439,10 +503,11 @@ FERRUM_API int ferrum_attention_latent(const void* q, int ldq, void* out, int ld
                          cudaGetErrorString(e));                                                                            \
         configured = s.bytes;                                                                                               \
       }                                                                                                                     \
-      launch_kernel(attention_latent_kernel<T, DVI_, TH_, HW_>, dim3((unsigned)ctas), dim3(LAT_WARPS * 32), (size_t)s.bytes, \
+      launch_kernel(attention_latent_kernel<T, DVI_, TH_, HW_>, dim3((unsigned)ctas, part ? split_slots : 1),               \
+                    dim3(LAT_WARPS * 32), (size_t)s.bytes,                                                                  \
                     stream, (const T*)q, ldq, (T*)out, ldo, gate, positions, q_start, n_reqs, block_table, table_width,     \
                     (const T*)plane, page_stride, page_size, H, Dk, Dv, scale, window, err_flag, vec, TK, s.DK8, s.off_q,    \
-                    s.off_p, s.off_row);                                                                                    \
+                    s.off_p, s.off_row, part, split_slots);                                                                 \
     });                                                                                                                     \
   } while (0)
 #define LAT_SHAPES(DVI_)                               \
@@ -461,5 +526,99 @@ FERRUM_API int ferrum_attention_latent(const void* q, int ldq, void* out, int ld
 #undef LAT_SHAPES
 #undef LAT_LAUNCH
   FERRUM_CHECK_LAUNCH("attention_latent");
+  if (part != nullptr) {
+    FERRUM_CHECK_ARG(H <= 65535, "latent attention: too many heads");
+    FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(attention_latent_combine_kernel<T>, dim3(n_tokens, H), dim3(32), 0, stream, (T*)out, ldo,
+                                                  part, gate, positions, H, Dv, window, split_slots));
+    FERRUM_CHECK_LAUNCH("attention_latent_combine");
+  }
+  return 0;
+}
+
+// ================================================================= one small product per head, few tokens
+// y[t, h * ldyh + n] = sum_k x[t, h * ldxh + k] * w[h][n][k] for n < N, k < K: every head has its own
+// [N, K] matrix (k contiguous).  For steps of a few tokens the time is the weights' read: a warp
+// owns one output feature of one head, reads its weight row once (8 bytes a lane where the rows
+// allow) and keeps up to HL_TOK tokens' sums, which the lanes fold in a butterfly; more tokens
+// take further passes over the (cached) row.  A sum walks k in an order that depends on K alone.
+constexpr int HL_WARPS = 8, HL_TOK = 8;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(HL_WARPS * 32)
+head_linear_kernel(const T* __restrict__ x, int ldx, int ldxh, const T* __restrict__ w, T* __restrict__ y, int ldy, int ldyh,
+                   int M, int N, int K) {
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * HL_WARPS + warp, h = blockIdx.y;
+  if (n >= N) return;
+  const T* wr = w + ((size_t)h * N + n) * K;
+  for (int t0 = 0; t0 < M; t0 += HL_TOK) {
+    float acc[HL_TOK];
+#pragma unroll
+    for (int i = 0; i < HL_TOK; ++i) acc[i] = 0.f;
+    if constexpr (VEC) {
+      for (int k = lane * 4; k < K; k += 128) {
+        float wv[4];
+        if constexpr (sizeof(T) == 4) {
+          const float4 u = *reinterpret_cast<const float4*>(wr + k);
+          wv[0] = u.x; wv[1] = u.y; wv[2] = u.z; wv[3] = u.w;
+        } else {
+          const uint2 u = *reinterpret_cast<const uint2*>(wr + k);
+          const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) wv[j] = to_f32<T>(e[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < HL_TOK; ++i) {
+          if (t0 + i < M) {
+            const T* xr = x + (size_t)(t0 + i) * ldx + (size_t)h * ldxh + k;
+            float xv[4];
+            if constexpr (sizeof(T) == 4) {
+              const float4 u = *reinterpret_cast<const float4*>(xr);
+              xv[0] = u.x; xv[1] = u.y; xv[2] = u.z; xv[3] = u.w;
+            } else {
+              const uint2 u = *reinterpret_cast<const uint2*>(xr);
+              const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) xv[j] = to_f32<T>(e[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float wv = to_f32<T>(wr[k]);
+#pragma unroll
+        for (int i = 0; i < HL_TOK; ++i)
+          if (t0 + i < M) acc[i] = fmaf(to_f32<T>(x[(size_t)(t0 + i) * ldx + (size_t)h * ldxh + k]), wv, acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < HL_TOK; ++i) {
+      const float s = warp_sum(acc[i]);
+      if (lane == 0 && t0 + i < M) y[(size_t)(t0 + i) * ldy + (size_t)h * ldyh + n] = from_f32<T>(s);
+    }
+  }
+}
+
+FERRUM_API int ferrum_head_linear_max_tokens() { return 64; }
+
+FERRUM_API int ferrum_head_linear(const void* x, int ldx, int ldxh, const void* w, void* y, int ldy, int ldyh, int dtype, int M,
+                                  int H, int N, int K, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(M >= 0 && H > 0 && H <= 65535 && N > 0 && K > 0, "head linear: bad sizes M=%d H=%d N=%d K=%d", M, H, N, K);
+  FERRUM_CHECK_ARG(ldxh >= 0 && ldyh >= N && ldx >= (H - 1) * ldxh + K && ldy >= (H - 1) * ldyh + N, "head linear: a stride is too short");
+  if (M == 0) return 0;
+  const int esize = dtype == FERRUM_F32 ? 4 : 2;
+  const int al = esize == 4 ? 16 : 8;
+  const bool vec = K % 4 == 0 && ldx % 4 == 0 && ldxh % 4 == 0 && ((uintptr_t)x % al) == 0 && ((uintptr_t)w % al) == 0;
+  const dim3 grid((N + HL_WARPS - 1) / HL_WARPS, H);
+  FERRUM_DISPATCH_DTYPE(dtype, T, {
+    if (vec) launch_kernel(head_linear_kernel<T, true>, grid, dim3(HL_WARPS * 32), 0, stream, (const T*)x, ldx, ldxh, (const T*)w, (T*)y, ldy, ldyh, M, N, K);
+    else launch_kernel(head_linear_kernel<T, false>, grid, dim3(HL_WARPS * 32), 0, stream, (const T*)x, ldx, ldxh, (const T*)w, (T*)y, ldy, ldyh, M, N, K);
+  });
+  FERRUM_CHECK_LAUNCH("head_linear");
   return 0;
 }

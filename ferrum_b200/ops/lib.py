@@ -158,6 +158,13 @@ def _gemm_work(x, w, out, M, N, K, products=1):
                  2.0 * products * M * N * K)
 
 
+def _bytes_work(*tensors_rows):
+    """(bytes, 0 flops) for the profile: (tensor, rows) pairs give rows x row bytes each."""
+    global _work
+    if _profile is not None:
+        _work = (sum(int(r) * t.shape[-1] * t.element_size() for t, r in tensors_rows if t is not None), 0.0)
+
+
 def _ptr(t):
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
 
@@ -242,6 +249,8 @@ def rmsnorm(x, weight, out, eps, rows=None, n_rows=None, partials=None, groups=1
         raise KernelError("rmsnorm: shapes do not agree")
     if rows is not None:
         _need(rows, torch.int32, "rows", 1)
+    if partials is None:
+        _bytes_work((x, n_rows), (out, n_rows))
     if groups != 1:
         if partials is not None:
             raise KernelError("rmsnorm: a grouped norm takes no pending product")
@@ -368,6 +377,9 @@ def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_si
         _need(kv_plane, qkv.dtype, "kv_plane")
     if not block_table.is_contiguous():
         raise KernelError("rope: block_table must be contiguous")
+    global _work
+    if _profile is not None and partials is None:
+        _work = (n_tokens * (2 * Hq + (3 * Hkv if write_kv else 0)) * D * qkv.element_size(), 0.0)
     _check(lib().ferrum_rope_cache_write(_ptr(qkv), dtype_code(qkv.dtype), c_int(n_tokens), c_int(qkv.stride(0)),
                                          _ptr(positions), _ptr(req_of_token), _ptr(block_table),
                                          c_int(block_table.shape[1]), _ptr(cos_sin if R else None),
@@ -414,6 +426,34 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
 def attention_flash_supported(dtype, D, page_stride=0):
     """True when the tensor-core attention kernel is built for this dtype and head size."""
     return dtype in SIXTEEN_BIT and bool(lib().ferrum_attention_flash_supported(c_int(D), c_int(16)))
+
+
+def attention_work(ctx, Hq, Hkv, D, window, esize):
+    """(bytes, flops) of causal attention for the step in `ctx`, for the profile: every visible key
+    and value row once, the queries and outputs; two products per (query, visible key) pair."""
+    keys, pairs = visible_keys(ctx, window)
+    return (keys * 2 * Hkv * D * esize + 2 * ctx.n_tokens * Hq * D * esize, 4.0 * pairs * Hq * D)
+
+
+def visible_keys(ctx, window):
+    """(cached rows the step's requests read, (query, visible key) pairs) of the step in `ctx`."""
+    keys = pairs = 0
+    for p, n in zip(ctx.h_pos0, ctx.h_q_len):
+        keys += min(p + n, window + n - 1) if window > 0 else p + n
+        for i in range(n):
+            pairs += min(p + i + 1, window) if window > 0 else p + i + 1
+    return keys, pairs
+
+
+def set_work(work):
+    """A part that knows its kernel's work tells the profile before the launch."""
+    global _work
+    if _profile is not None:
+        _work = work
+
+
+def profiling():
+    return _profile is not None
 
 
 def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o,
@@ -507,6 +547,7 @@ def norm_pair_shift(x, w1, w2, shift, a, m, b, n_tokens, ctx, state, stage, grou
         _need(shift, torch.float32, "shift", 1); _need(state, torch.float32, "state", 2); _need(stage, torch.float32, "stage", 2)
         if state.shape[1] != E or stage.shape[1] != E or stage.shape[0] < ctx.n_reqs or not state.is_contiguous():
             raise KernelError("norm_pair_shift: state and stage rows must have E elements")
+    _bytes_work((x, n_tokens), (a, n_tokens), (m, n_tokens), (b, n_tokens))
     _check(lib().ferrum_norm_pair_shift(_ptr(x), _ptr(w1), _ptr(w2), _ptr(shift), _ptr(a), _ptr(m), _ptr(b), dtype_code(a.dtype),
                                         c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.req_of_token), _ptr(ctx.q_start),
                                         _ptr(ctx.slots), _ptr(state), _ptr(stage), c_int(E), c_int(groups), c_float(eps),
@@ -522,6 +563,9 @@ def bias_glu(gu, bias_gate, bias_up, act, n_tokens, F, kind="silu"):
     for bias in (bias_gate, bias_up):
         if bias is not None:
             _need(bias, torch.float32, "bias", 1)
+    global _work
+    if _profile is not None:
+        _work = (n_tokens * F * (8 + act.element_size()), 0.0)
     _check(lib().ferrum_bias_glu(_ptr(gu), c_int(gu.stride(0)), _ptr(bias_gate), _ptr(bias_up), _ptr(act), dtype_code(act.dtype),
                                  c_int(act.stride(0)), c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), _stream()), "bias_glu")
 
@@ -535,6 +579,9 @@ def gated_residual(x, n_tokens, y1, g1, c1, y2=None, c2=None, g2=None, c3=None, 
         if t is not None:
             _need(t, torch.float32, "operand", 2)
     ld = lambda t: c_int(t.stride(0) if t is not None else 0)
+    global _work
+    if _profile is not None:
+        _work = (n_tokens * x.shape[1] * 4 * (2 + sum(t is not None for t in (y1, g1, y2, g2))), 0.0)
     _check(lib().ferrum_gated_residual(_ptr(x), c_int(n_tokens), c_int(x.shape[1]), _ptr(y1), ld(y1), _ptr(g1), ld(g1), _ptr(c1),
                                        _ptr(y2), ld(y2), _ptr(c2), _ptr(g2), ld(g2), _ptr(c3),
                                        _ptr(ctx.req_of_token if state is not None else None),
@@ -553,6 +600,9 @@ def latent_prep(proj, n_tokens, off_q, q_rank, wq, off_kv, kv_rank, rot_dim, wkv
     if off_kv >= 0:
         _need(plane, cq.dtype, "plane")
     cos_sin = rot.cos_sin if rot is not None else None
+    global _work
+    if _profile is not None:
+        _work = (n_tokens * (proj.shape[1] * 4 + (q_rank + (kv_rank + rot_dim if off_kv >= 0 else 0)) * cq.element_size()), 0.0)
     _check(lib().ferrum_latent_prep(_ptr(proj), c_int(proj.stride(0)), c_int(n_tokens), c_int(off_q), c_int(q_rank), _ptr(wq),
                                     c_int(off_kv), c_int(kv_rank), c_int(rot_dim), _ptr(wkv), c_int(off_gate), c_int(n_gate),
                                     _ptr(ctx.positions), _ptr(ctx.req_of_token), _ptr(block_table), c_int(block_table.shape[1]),
@@ -573,20 +623,55 @@ def latent_q_rope(q, qf, n_tokens, positions, rot, H, Dn, Rr, R, err):
                                       _ptr(err), _stream()), "latent_q_rope")
 
 
+@functools.lru_cache(maxsize=1)
+def attention_latent_split():
+    """Keys per split of the latent attention kernel's split mode."""
+    return int(lib().ferrum_attention_latent_split())
+
+
 def attention_latent(qf, out, gate, n_tokens, ctx, block_table, plane, page_stride, page_size, H, Dk, Dv, scale, window,
-                     single_tokens):
+                     single_tokens, part=None, split_slots=0):
     """Attention of every token over its request's cached rows of Dk elements, whose first Dv
-    elements are the values; qf: heads of Dk, out: heads of Dv, times gate[t, h] (latent.cu)."""
+    elements are the values; qf: heads of Dk, out: heads of Dv, times gate[t, h] (latent.cu).
+    With `part` (float32, n_tokens * H * split_slots * (Dv + 2) elements; single tokens only) every
+    token's keys are cut at multiples of `attention_latent_split()` among split_slots CTAs and folded
+    by a second launch."""
+    if part is not None:
+        _need(part, torch.float32, "part")
+        if part.numel() < n_tokens * H * split_slots * (Dv + 2):
+            raise KernelError("attention_latent: the partials buffer is too small")
     _need(qf, None, "qf", 2); _need(out, qf.dtype, "out", 2); _need(plane, qf.dtype, "plane")
     if gate is not None:
         _need(gate, torch.float32, "gate", 2)
     global _work
     if _profile is not None:
-        keys = sum(min(p + n, window + n) if window > 0 else p + n for p, n in zip(ctx.h_pos0, ctx.h_q_len))
-        pairs = sum(n * (min(p + n, window) if window > 0 else p + (n + 1) / 2) for p, n in zip(ctx.h_pos0, ctx.h_q_len))
+        keys, pairs = visible_keys(ctx, window)
         _work = (keys * Dk * plane.element_size() + n_tokens * H * (Dk + Dv) * qf.element_size(), 2.0 * pairs * H * (Dk + Dv))
     _check(lib().ferrum_attention_latent(_ptr(qf), c_int(qf.stride(0)), _ptr(out), c_int(out.stride(0)), dtype_code(qf.dtype),
                                          _ptr(gate), c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.q_start), c_int(ctx.n_reqs),
                                          _ptr(block_table), c_int(block_table.shape[1]), _ptr(plane), c_longlong(page_stride),
                                          c_int(page_size), c_int(H), c_int(Dk), c_int(Dv), c_float(scale), c_int(window),
-                                         c_int(1 if single_tokens else 0), _ptr(ctx.err), _stream()), "attention_latent")
+                                         c_int(1 if single_tokens else 0), _ptr(part), c_int(split_slots), _ptr(ctx.err),
+                                         _stream()), "attention_latent")
+    if part is not None:
+        globals()["launches"] += 1        # (the merge of the splits is a second kernel)
+
+
+@functools.lru_cache(maxsize=1)
+def head_linear_max_tokens():
+    return int(lib().ferrum_head_linear_max_tokens())
+
+
+def head_linear(x, x_head_stride, w, y, y_head_stride, n_tokens):
+    """y[t, h * y_head_stride + n] = sum_k x[t, h * x_head_stride + k] * w[h, n, k]: one small product
+    per head in one launch, for steps of a few tokens (latent.cu); w: [H, N, K] contiguous."""
+    _need(x, None, "x", 2); _need(y, x.dtype, "y", 2); _need(w, x.dtype, "w", 3)
+    if not w.is_contiguous():
+        raise KernelError("head_linear: w must be contiguous [H, N, K]")
+    H, N, K = w.shape
+    global _work
+    if _profile is not None:
+        _work = (w.numel() * w.element_size() + n_tokens * H * (N + K) * x.element_size(), 2.0 * n_tokens * H * N * K)
+    _check(lib().ferrum_head_linear(_ptr(x), c_int(x.stride(0)), c_int(x_head_stride), _ptr(w), _ptr(y), c_int(y.stride(0)),
+                                    c_int(y_head_stride), dtype_code(x.dtype), c_int(n_tokens), c_int(H), c_int(N), c_int(K),
+                                    _stream()), "head_linear")

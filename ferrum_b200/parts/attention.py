@@ -127,6 +127,8 @@ class PagedAttention(Mixer):
             if plan.n_slots:
                 part_o = ctx.buf("attn_part_o", (plan.n_slots * plan.bm * D,), torch.float32)
                 part_ml = ctx.buf("attn_part_ml", (plan.n_slots * plan.bm * 2,), torch.float32)
+            if ops.profiling():      # (a step with several classes counts the whole step's work for each)
+                ops.set_work(ops.attention_work(ctx, Hq, Hkv, D, self.window, qkv.element_size()))
             if plan.kind == "tc":
                 ops.attention_tc(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start, ctx.pos0,
                                  plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale, self.window, ctx.err)

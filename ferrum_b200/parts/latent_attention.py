@@ -22,8 +22,13 @@ from __future__ import annotations
 import torch
 
 from ..ops import lib as ops
+from . import attention_plan
 from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
 from .linear import RESIDUAL, STORE, STORE_F32, linear
+
+
+# Steps of single tokens cut every token's keys among CTAs while they bring fewer rows than this per SM.
+SPLIT_BELOW = 4
 
 
 class LatentAttention(Mixer):
@@ -63,7 +68,7 @@ class LatentAttention(Mixer):
         self.w_dq_weight = self.w_dkv_weight = self.w_g_weight = None
         # per head: U_k,h^T as [kv_rank, dim] (a linear map from the head's plain query part) and U_v,h as [vdim, kv_rank]
         self.w_uk_t = self.w_uk_weight.view(self.H, self.Dn, self.R).transpose(1, 2).contiguous()
-        self.w_uv_h = self.w_uv_weight.view(self.H, self.Dv, self.R)
+        self.w_uv_h = self.w_uv_weight.view(self.H, self.Dv, self.R)     # (a view: contiguous [H, vdim, kv_rank])
         self.w_uk_weight = None
 
     def cache_need(self):
@@ -88,13 +93,31 @@ class LatentAttention(Mixer):
         q = ctx.buf("lat_q", (cap, H * (Dn + Rr)), self.dtype)
         linear(cq, self.w_uq_weight, q, STORE, ctx, M=T)
         qf = ctx.buf("lat_qf", (cap, H * Dk), self.dtype)
-        for h in range(H):
-            linear(q[:, h * (Dn + Rr):h * (Dn + Rr) + Dn], self.w_uk_t[h], qf[:, h * Dk:h * Dk + R], STORE, ctx, M=T)
+        few = T <= ops.head_linear_max_tokens()      # a few tokens: every head's product in one launch
+        if few:
+            ops.head_linear(q, Dn + Rr, self.w_uk_t, qf, Dk, T)
+        else:
+            for h in range(H):
+                linear(q[:, h * (Dn + Rr):h * (Dn + Rr) + Dn], self.w_uk_t[h], qf[:, h * Dk:h * Dk + R], STORE, ctx, M=T)
         ops.latent_q_rope(q, qf, T, ctx.positions, self.rotary, H, Dn, Rr, R, ctx.err)
         o = ctx.buf("lat_o", (cap, H * R), self.dtype)
+        single = ctx.max_q_len == 1
+        part, slots = None, 0
+        if single and T * -(-H // 8) < SPLIT_BELOW * attention_plan.sm_count():
+            # few single tokens: their key ranges are cut among CTAs.  The number of slots depends on the
+            # batch's sizes alone while a CUDA graph is captured or replayed (the longest context the table holds).
+            split = ops.attention_latent_split()
+            longest = table.shape[1] * cache.page_size if ctx.fixed_shapes else ctx.max_kv_len
+            if self.window > 0:
+                longest = min(longest, self.window + split)
+            slots = longest // split + 2
+            part = ctx.buf("lat_part", (T * H * slots * (R + 2),), torch.float32)
         ops.attention_latent(qf, o, gate, T, ctx, table, cache.plane, cache.page_stride, cache.page_size, H, Dk, R,
-                             self.scale, self.window, single_tokens=ctx.max_q_len == 1)
+                             self.scale, self.window, single_tokens=single, part=part, split_slots=slots)
         ov = ctx.buf("lat_ov", (cap, H * Dv), self.dtype)
-        for h in range(H):
-            linear(o[:, h * R:(h + 1) * R], self.w_uv_h[h], ov[:, h * Dv:(h + 1) * Dv], STORE, ctx, M=T)
+        if few:
+            ops.head_linear(o, R, self.w_uv_h, ov, Dv, T)
+        else:
+            for h in range(H):
+                linear(o[:, h * R:(h + 1) * R], self.w_uv_h[h], ov[:, h * Dv:(h + 1) * Dv], STORE, ctx, M=T)
         linear(ov, self.w_o_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)

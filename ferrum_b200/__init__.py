@@ -1,4 +1,4 @@
-"""ferrum_b200: a single-GPU Llama inference engine for NVIDIA B200 (sm_100a).
+"""ferrum_b200: a single-GPU inference engine (Llama, Ruperax) for NVIDIA B200 (sm_100a).
 
 Everything between a request's token ids and its next token: typed configuration and a
 model registry, safetensors/GGUF weights, a model put together from parts, a paged cache

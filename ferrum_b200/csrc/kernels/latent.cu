@@ -419,44 +419,61 @@ attention_latent_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
   }
 }
 
-// Folds the splits of every (token, head) in ascending key order and applies the gate: one warp each.
+// Folds the splits of every (token, head) and applies the gate: one block of four warps each.  The
+// first warp reads every split's (max, sum), takes the overall maximum and leaves each split's factor
+// exp(max_s - max) in shared memory; then thread d adds the splits' weighted values of element d,
+// d + 128, ... in ascending key order (independent loads: the splits are not walked as a chain).
+constexpr int LAT_COMB_THREADS = 128, LAT_COMB_MAX = 1024;
 template <typename T>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(LAT_COMB_THREADS)
 attention_latent_combine_kernel(T* __restrict__ out, int ldo, const float* __restrict__ part, const float* __restrict__ gate,
                                 const int* __restrict__ positions, int H, int Dv, int window, int split_slots) {
+  __shared__ float factor[LAT_COMB_MAX];
+  __shared__ float total;
   pdl_launch();
   pdl_wait();
-  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+  const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int n = min(pos / LAT_SPLIT - lo / LAT_SPLIT + 1, split_slots);
+  const int n = min(min(pos / LAT_SPLIT - lo / LAT_SPLIT + 1, split_slots), LAT_COMB_MAX);
   const float* base = part + ((size_t)t * H + h) * split_slots * (Dv + 2);
-  float M = -INFINITY, L = 0.f, O[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) O[i] = 0.f;
-  for (int s = 0; s < n; ++s) {
-    const float* p = base + (size_t)s * (Dv + 2);
-    const float mb = p[0], lb = p[1];
-    const float m_new = fmaxf(M, mb);
-    const float fa = M == -INFINITY ? 0.f : expf(M - m_new);
-    const float fb = mb == -INFINITY ? 0.f : expf(mb - m_new);
-    L = L * fa + lb * fb;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int d = lane + 32 * i;
-      if (d < Dv) O[i] = O[i] * fa + p[2 + d] * fb;
+  if (threadIdx.x < 32) {
+    float mx = -INFINITY;
+    for (int s = threadIdx.x; s < n; s += 32) mx = fmaxf(mx, base[(size_t)s * (Dv + 2)]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int s = threadIdx.x; s < n; s += 32) {
+      const float ms = base[(size_t)s * (Dv + 2)];
+      const float f = ms == -INFINITY ? 0.f : expf(ms - mx);
+      factor[s] = f;
+      sum += base[(size_t)s * (Dv + 2) + 1] * f;
     }
-    M = m_new;
+    sum = warp_sum(sum);
+    if (threadIdx.x == 0) total = sum;
   }
+  __syncthreads();
+  const float L = total;
   const float f = (L > 0.f ? 1.0f / L : 0.f) * (gate != nullptr ? gate[(size_t)t * H + h] : 1.0f);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int d = lane + 32 * i;
-    if (d < Dv) out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<T>(O[i] * f);
+  for (int d = threadIdx.x; d < Dv; d += LAT_COMB_THREADS) {
+    float o = 0.f;
+    for (int s = 0; s < n; ++s) o = fmaf(base[(size_t)s * (Dv + 2) + 2 + d], factor[s], o);
+    out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<T>(o * f);
   }
 }
 
 FERRUM_API int ferrum_attention_latent_split() { return LAT_SPLIT; }
+
+// out[t, h] = gate[t, h] * (the fold of the splits' partials [t][h][slot][Dv + 2] in ascending key order).
+FERRUM_API int ferrum_attention_latent_combine(void* out, int ldo, int dtype, const float* part, const float* gate, int n_tokens,
+                                               const int* positions, int H, int Dv, int window, int split_slots, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && H > 0 && H <= 65535 && Dv > 0 && split_slots > 0 && split_slots <= LAT_COMB_MAX && part != nullptr,
+                   "latent attention merge: bad arguments (at most %d splits)", LAT_COMB_MAX);
+  if (n_tokens == 0) return 0;
+  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(attention_latent_combine_kernel<T>, dim3(n_tokens, H), dim3(LAT_COMB_THREADS), 0, stream, (T*)out, ldo,
+                                                part, gate, positions, H, Dv, window, split_slots));
+  FERRUM_CHECK_LAUNCH("attention_latent_combine");
+  return 0;
+}
 
 constexpr int LAT_MAX_DK = 1024, LAT_MAX_DV = 512, LAT_SMEM_LIMIT = 200 * 1024;
 
@@ -526,12 +543,7 @@ FERRUM_API int ferrum_attention_latent(const void* q, int ldq, void* out, int ld
 #undef LAT_SHAPES
 #undef LAT_LAUNCH
   FERRUM_CHECK_LAUNCH("attention_latent");
-  if (part != nullptr) {
-    FERRUM_CHECK_ARG(H <= 65535, "latent attention: too many heads");
-    FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(attention_latent_combine_kernel<T>, dim3(n_tokens, H), dim3(32), 0, stream, (T*)out, ldo,
-                                                  part, gate, positions, H, Dv, window, split_slots));
-    FERRUM_CHECK_LAUNCH("attention_latent_combine");
-  }
+  if (part != nullptr) return ferrum_attention_latent_combine(out, ldo, dtype, part, gate, n_tokens, positions, H, Dv, window, split_slots, stream);
   return 0;
 }
 

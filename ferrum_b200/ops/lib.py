@@ -630,9 +630,11 @@ def attention_latent_split():
 
 
 def attention_latent(qf, out, gate, n_tokens, ctx, block_table, plane, page_stride, page_size, H, Dk, Dv, scale, window,
-                     single_tokens, part=None, split_slots=0):
+                     single_tokens, part=None, split_slots=0, tensor_cores=None):
     """Attention of every token over its request's cached rows of Dk elements, whose first Dv
     elements are the values; qf: heads of Dk, out: heads of Dv, times gate[t, h] (latent.cu).
+    tensor_cores: None picks the mma.sync kernel where it takes the shape (16-bit storage, Dk a
+    multiple of 16, Dv of 32), else the CUDA-core kernel; False forces the latter.
     With `part` (float32, n_tokens * H * split_slots * (Dv + 2) elements; single tokens only) every
     token's keys are cut at multiples of `attention_latent_split()` among split_slots CTAs and folded
     by a second launch."""
@@ -647,14 +649,30 @@ def attention_latent(qf, out, gate, n_tokens, ctx, block_table, plane, page_stri
     if _profile is not None:
         keys, pairs = visible_keys(ctx, window)
         _work = (keys * Dk * plane.element_size() + n_tokens * H * (Dk + Dv) * qf.element_size(), 2.0 * pairs * H * (Dk + Dv))
-    _check(lib().ferrum_attention_latent(_ptr(qf), c_int(qf.stride(0)), _ptr(out), c_int(out.stride(0)), dtype_code(qf.dtype),
-                                         _ptr(gate), c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.q_start), c_int(ctx.n_reqs),
-                                         _ptr(block_table), c_int(block_table.shape[1]), _ptr(plane), c_longlong(page_stride),
-                                         c_int(page_size), c_int(H), c_int(Dk), c_int(Dv), c_float(scale), c_int(window),
-                                         c_int(1 if single_tokens else 0), _ptr(part), c_int(split_slots), _ptr(ctx.err),
-                                         _stream()), "attention_latent")
+    args = (_ptr(qf), c_int(qf.stride(0)), _ptr(out), c_int(out.stride(0)), dtype_code(qf.dtype),
+            _ptr(gate), c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.q_start), c_int(ctx.n_reqs),
+            _ptr(block_table), c_int(block_table.shape[1]), _ptr(plane), c_longlong(page_stride),
+            c_int(page_size), c_int(H), c_int(Dk), c_int(Dv), c_float(scale), c_int(window),
+            c_int(1 if single_tokens else 0), _ptr(part), c_int(split_slots), _ptr(ctx.err), _stream())
+    if tensor_cores is None:
+        tensor_cores = attention_latent_mma_supported(qf, out, plane, page_stride, Dk, Dv)
+    if tensor_cores:
+        _check(lib().ferrum_attention_latent_mma(*args), "attention_latent_mma")
+        if part is not None:
+            _check(lib().ferrum_attention_latent_combine(_ptr(out), c_int(out.stride(0)), dtype_code(out.dtype), _ptr(part), _ptr(gate),
+                                                         c_int(n_tokens), _ptr(ctx.positions), c_int(H), c_int(Dv), c_int(window),
+                                                         c_int(split_slots), _stream()), "attention_latent_combine")
+        return
+    _check(lib().ferrum_attention_latent(*args), "attention_latent")
     if part is not None:
         globals()["launches"] += 1        # (the merge of the splits is a second kernel)
+
+
+def attention_latent_mma_supported(qf, out, plane, page_stride, Dk, Dv):
+    """True where the tensor-core kernel (attention_latent_mma.cu) takes the shape and the pointers."""
+    return qf.dtype in SIXTEEN_BIT and bool(lib().ferrum_attention_latent_mma_supported(
+        dtype_code(qf.dtype), c_int(Dk), c_int(Dv), c_int(qf.stride(0)), c_int(out.stride(0)), c_longlong(page_stride),
+        _ptr(qf), _ptr(out), _ptr(plane)))
 
 
 @functools.lru_cache(maxsize=1)
@@ -662,14 +680,30 @@ def head_linear_max_tokens():
     return int(lib().ferrum_head_linear_max_tokens())
 
 
+def head_linear_mma_supported(x, x_head_stride, w, y, y_head_stride):
+    """True where the tensor-core kernel for many tokens takes the operands (16-bit, 16-byte rows)."""
+    return x.dtype in SIXTEEN_BIT and bool(lib().ferrum_head_linear_mma_supported(
+        dtype_code(x.dtype), c_int(w.shape[2]), c_int(x.stride(0)), c_int(x_head_stride), c_int(y.stride(0)), c_int(y_head_stride),
+        _ptr(x), _ptr(w), _ptr(y)))
+
+
 def head_linear(x, x_head_stride, w, y, y_head_stride, n_tokens):
     """y[t, h * y_head_stride + n] = sum_k x[t, h * x_head_stride + k] * w[h, n, k]: one small product
-    per head in one launch, for steps of a few tokens (latent.cu); w: [H, N, K] contiguous."""
+    per head in one launch; w: [H, N, K] contiguous.  Up to `head_linear_max_tokens()` tokens on the
+    CUDA cores (latent.cu: the time is the weights' read); more tokens on mma.sync where
+    `head_linear_mma_supported` (attention_latent_mma.cu)."""
     _need(x, None, "x", 2); _need(y, x.dtype, "y", 2); _need(w, x.dtype, "w", 3)
     if not w.is_contiguous():
         raise KernelError("head_linear: w must be contiguous [H, N, K]")
     H, N, K = w.shape
-    global _work
+    if n_tokens > head_linear_max_tokens():
+        global _work
+        if _profile is not None:
+            _work = (w.numel() * w.element_size() + n_tokens * H * (N + K) * x.element_size(), 2.0 * n_tokens * H * N * K)
+        _check(lib().ferrum_head_linear_mma(_ptr(x), c_int(x.stride(0)), c_int(x_head_stride), _ptr(w), _ptr(y), c_int(y.stride(0)),
+                                            c_int(y_head_stride), dtype_code(x.dtype), c_int(n_tokens), c_int(H), c_int(N), c_int(K),
+                                            _stream()), "head_linear_mma")
+        return
     if _profile is not None:
         _work = (w.numel() * w.element_size() + n_tokens * H * (N + K) * x.element_size(), 2.0 * n_tokens * H * N * K)
     _check(lib().ferrum_head_linear(_ptr(x), c_int(x.stride(0)), c_int(x_head_stride), _ptr(w), _ptr(y), c_int(y.stride(0)),

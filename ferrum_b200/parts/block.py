@@ -5,7 +5,11 @@ pass").  The two residual sums happen inside the parts' last kernels, in float32
 """
 from __future__ import annotations
 
-from .base import FeedForward, Mixer, Norm, Part
+import torch
+
+from ..ops import lib as ops
+from .base import CacheNeed, FeedForward, Mixer, Norm, ParamSpec, Part, StateNeed
+from .linear import STORE_F32, linear
 
 
 class PreNormBlock(Part):
@@ -56,7 +60,6 @@ class ParallelGatedBlock(Part):
         self._rg2_fused = False
 
     def param_specs(self):
-        from .base import ParamSpec
         E = self.width
         out = {"norm1.weight": ParamSpec((E,), kind="vector", init="ones_normal"),
                "rg1.weight": ParamSpec((E, E)), "rg1.bias": ParamSpec((E,), kind="vector")}
@@ -74,13 +77,11 @@ class ParallelGatedBlock(Part):
         return out
 
     def cache_need(self):
-        from .base import CacheNeed, StateNeed
         need = self.mixer.cache_need()
         if not self.token_shift:
             return need
         if need.state is not None:
             raise ValueError("the block's token shift and its mixer both want the run's state")
-        import torch
         return CacheNeed(paged=need.paged, state=StateNeed((self.width,), torch.float32))
 
     def finalize(self):
@@ -93,9 +94,6 @@ class ParallelGatedBlock(Part):
             self.w_rg2_weight = None
 
     def forward(self, h, ctx, cache):
-        import torch
-        from ..ops import lib as ops
-        from .linear import STORE_F32, linear
         ctx.flush_residual()
         T, E, cap = ctx.n_tokens, self.width, ctx.token_capacity
         a = ctx.buf("pgb_a", (cap, E), self.dtype)

@@ -29,6 +29,7 @@ from .linear import RESIDUAL, STORE, STORE_F32, linear
 
 # Steps of single tokens cut every token's keys among CTAs while they bring fewer rows than this per SM.
 SPLIT_BELOW = 4
+MAX_SPLITS = 1024       # what the merge kernel folds per (token, head)
 
 
 class LatentAttention(Mixer):
@@ -93,8 +94,8 @@ class LatentAttention(Mixer):
         q = ctx.buf("lat_q", (cap, H * (Dn + Rr)), self.dtype)
         linear(cq, self.w_uq_weight, q, STORE, ctx, M=T)
         qf = ctx.buf("lat_qf", (cap, H * Dk), self.dtype)
-        few = T <= ops.head_linear_max_tokens()      # a few tokens: every head's product in one launch
-        if few:
+        few = T <= ops.head_linear_max_tokens()      # every head's product in one launch: a few tokens on the CUDA cores ...
+        if few or ops.head_linear_mma_supported(q, Dn + Rr, self.w_uk_t, qf, Dk):     # ... many on the tensor cores
             ops.head_linear(q, Dn + Rr, self.w_uk_t, qf, Dk, T)
         else:
             for h in range(H):
@@ -111,11 +112,14 @@ class LatentAttention(Mixer):
             if self.window > 0:
                 longest = min(longest, self.window + split)
             slots = longest // split + 2
-            part = ctx.buf("lat_part", (T * H * slots * (R + 2),), torch.float32)
+            if slots <= MAX_SPLITS:
+                part = ctx.buf("lat_part", (T * H * slots * (R + 2),), torch.float32)
+            else:
+                slots = 0
         ops.attention_latent(qf, o, gate, T, ctx, table, cache.plane, cache.page_stride, cache.page_size, H, Dk, R,
                              self.scale, self.window, single_tokens=single, part=part, split_slots=slots)
         ov = ctx.buf("lat_ov", (cap, H * Dv), self.dtype)
-        if few:
+        if few or ops.head_linear_mma_supported(o, R, self.w_uv_h, ov, Dv):
             ops.head_linear(o, R, self.w_uv_h, ov, Dv, T)
         else:
             for h in range(H):

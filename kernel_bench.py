@@ -7,6 +7,8 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py attn_prefill [--tokens 2048]
     python kernel_bench.py gemm --tokens 8 --n 6144 --k 4096 [--epilogue store|residual|swiglu] [--copies 8]
     python kernel_bench.py gemm|attn_decode|attn_prefill ... --dtype fp32    (the CUDA-core kernels of the 32-bit path)
+    python kernel_bench.py latent_decode|latent_prefill [--hq 16] [--kv-rank 512] [--rot-dim 64] [--window W] [--cuda-cores]
+    python kernel_bench.py head_linear --tokens 8 --hq 16 --n 512 --k 128
     python kernel_bench.py rmsnorm|rope --tokens 8
     python kernel_bench.py step --tokens 2048 [--layers 2] [--dtype bf16|fp16|fp32]   (one prompt portion through the model)
     FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
@@ -31,7 +33,12 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemm", "rmsnorm", "rope", "step", "timeline"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "latent_decode", "latent_prefill", "head_linear", "gemm", "rmsnorm",
+                                       "rope", "step", "timeline"])
+    ap.add_argument("--kv-rank", type=int, default=512, help="latent_*: elements of the cached latent (the values)")
+    ap.add_argument("--rot-dim", type=int, default=64, help="latent_*: rotated key elements behind the latent")
+    ap.add_argument("--window", type=int, default=0, help="latent_*: keys a query looks back over (0: all)")
+    ap.add_argument("--cuda-cores", action="store_true", help="latent_*: the CUDA-core kernel also where the tensor-core one applies")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=8)
@@ -110,6 +117,44 @@ def main():
         kv_bytes = R * ctx_len * 2 * Hkv * D * esize
         flops = 4.0 * Hq * D * (ctx_len * qlen if decode else qlen * qlen / 2) * R
         work = {"bytes": kv_bytes + 2 * T * Hq * D * esize, "flops": flops, "bound": "hbm" if decode else "tensor"}
+    elif args.kernel in ("latent_decode", "latent_prefill"):
+        # attention over cached rows of kv_rank + rot_dim elements, --hq heads sharing them
+        decode = args.kernel == "latent_decode"
+        R = args.batch if decode else 1
+        qlen = 1 if decode else args.tokens
+        ctx_len = args.context if decode else args.tokens
+        Rk, Dk = args.kv_rank, args.kv_rank + args.rot_dim
+        width = (ctx_len + ps - 1) // ps
+        n_pages = R * width
+        planes = [torch.randn(n_pages, ps, Dk, device=dev, generator=gen).mul_(0.5).to(td) for _ in range(args.layers)]
+        perm = torch.randperm(n_pages).view(R, width).tolist()
+        ctx = StepContext(dev, max(16, R * qlen), R, [width])
+        ctx.fill([StepEntry(r, ctx_len - qlen, [1] * qlen) for r in range(R)], [perm])
+        T = R * qlen
+        qf = torch.randn(T, Hq * Dk, device=dev, generator=gen).mul_(0.2).to(td)
+        out = torch.empty(T, Hq * Rk, device=dev, dtype=td)
+        gate = torch.rand(T, Hq, device=dev, generator=gen)
+        table = ctx.block_tables[0]
+        part, slots = None, 0
+        if decode and T * -(-Hq // 8) < 4 * ops.sm_count():
+            split = ops.attention_latent_split()
+            longest = min(ctx_len, args.window + split) if args.window else ctx_len
+            slots = longest // split + 2
+            part = torch.empty(T * Hq * slots * (Rk + 2), device=dev)
+        runs = [lambda pl=pl: ops.attention_latent(qf, out, gate, T, ctx, table, pl, pl.stride(0), ps, Hq, Dk, Rk, Dk ** -0.5, args.window,
+                                                   decode, part=part, split_slots=slots, tensor_cores=False if args.cuda_cores else None)
+                for pl in planes]
+        keys, pairs = ops.visible_keys(ctx, args.window)
+        work = {"bytes": keys * Dk * esize + T * Hq * (Dk + Rk) * esize, "flops": 2.0 * pairs * Hq * (Dk + Rk),
+                "bound": "hbm" if decode else "tensor"}
+    elif args.kernel == "head_linear":
+        # one small product per head: [tokens, n] = [tokens, k] x [n, k]^T for each of --hq heads
+        M, N, K = args.tokens, args.n, args.k
+        x = torch.randn(M, Hq * K, device=dev, generator=gen).to(td)
+        y = torch.empty(M, Hq * N, device=dev, dtype=td)
+        weights = [torch.randn(Hq, N, K, device=dev, generator=gen).mul_(0.05).to(td) for _ in range(args.copies)]
+        runs = [lambda w=w: ops.head_linear(x, K, w, y, N, M) for w in weights]
+        work = {"bytes": Hq * N * K * esize + M * Hq * (N + K) * esize, "flops": 2.0 * M * Hq * N * K, "bound": "hbm" if M <= 128 else "tensor"}
     elif args.kernel == "gemm":
         M, N, K = args.tokens, args.n, args.k
         dual = args.epilogue == "swiglu"

@@ -144,6 +144,28 @@ def test_biased_glu_and_gated_sum(cuda):
     assert (x.double() - ref).abs().max().item() < 1e-5 and (x2.double() - ref1).abs().max().item() < 1e-5
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,H,N,K", [(5, 3, 22, 10), (64, 2, 7, 37), (9, 16, 128, 64), (70, 3, 24, 16), (300, 5, 200, 72), (129, 2, 130, 8)])
+def test_one_product_per_head(cuda, dtype, M, H, N, K):
+    """y[t, h, :] = W_h x[t, h, :] for every head in one launch: few tokens (CUDA cores), many
+    (tensor cores in 16-bit), inside wider rows."""
+    from ferrum_b200.ops import lib as ops
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    td = TD[dtype]
+    pad = 8
+    x = torch.randn(M, H * (K + pad), device="cuda", generator=g).to(td)
+    w = (torch.randn(H, N, K, device="cuda", generator=g) * 0.3).to(td)
+    y = torch.zeros(M, H * (N + 2), device="cuda", dtype=td)
+    if M > ops.head_linear_max_tokens() and not ops.head_linear_mma_supported(x, K + pad, w, y, N + 2):
+        pytest.skip("many tokens of this shape run as one product per head on the product kernels")
+    ops.head_linear(x, K + pad, w, y, N + 2, M)
+    ref = torch.einsum("thk,hnk->thn", x.double().view(M, H, K + pad)[:, :, :K], w.double())
+    got = y.double().view(M, H, N + 2)
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    assert (got[:, :, :N] - ref).abs().max().item() < tol * max(1.0, ref.abs().max().item())
+    assert got[:, :, N:].abs().max().item() == 0          # nothing written between the heads' outputs
+
+
 def attention_rows_reference(qf, rows, pos, H, Dk, Dv, scale, window, gate):
     """out[t, h] = gate * sum_j softmax_j(qf[t, h] . rows[j] * scale) rows[j, :Dv] over j in (pos - window, pos]."""
     out = np.zeros((len(pos), H, Dv))
@@ -158,7 +180,9 @@ def attention_rows_reference(qf, rows, pos, H, Dk, Dv, scale, window, gate):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,R,Rr,page,window", [(3, 24, 8, 8, 19), (5, 40, 0, 16, 64), (9, 100, 12, 32, 0), (2, 300, 20, 16, 130)])
+@pytest.mark.parametrize("H,R,Rr,page,window", [(3, 24, 8, 8, 19), (5, 40, 0, 16, 64), (9, 100, 12, 32, 0), (2, 300, 20, 16, 130),
+                                                (16, 64, 16, 16, 70), (5, 128, 32, 8, 0), (20, 96, 16, 32, 130), (2, 512, 64, 16, 19),
+                                                (1, 32, 0, 16, 64)])
 def test_attention_over_cached_rows_sees_exactly_its_window(cuda, dtype, H, R, Rr, page, window):
     """The attention kernel alone on rows written straight into pages that lie scattered in the
     pool.  One cached row is made to dominate: it is scaled up and every query points at it.
@@ -180,6 +204,8 @@ def test_attention_over_cached_rows_sees_exactly_its_window(cuda, dtype, H, R, R
     for lp in range(n_pages):
         chunk = rows_t[lp * page:(lp + 1) * page]
         plane[order[lp], :len(chunk)] = chunk
+    # 16-bit rows whose sizes the tensor-core kernel takes run on it; the others, and float32, on the CUDA cores
+    on_tensor_cores = dtype != "float32" and (R + Rr) % 16 == 0 and R % 32 == 0
     for pos0, n in ((n_keys - 40, 40), (n_keys - 1, 1), (hot + max(window, 1) - 2, 3)):
         ctx = make_ctx([(pos0, n)], widths=[[list(order)]])
         pos = list(range(pos0, pos0 + n))
@@ -194,8 +220,14 @@ def test_attention_over_cached_rows_sees_exactly_its_window(cuda, dtype, H, R, R
                 slots = (min(n_keys, window + ops.attention_latent_split()) if window else n_keys) // ops.attention_latent_split() + 2
                 part = torch.full((n * H * slots * (R + 2),), float("nan"), device="cuda")
             out.zero_()
+            assert ops.attention_latent_mma_supported(qf_t, out, plane, plane.stride(0), Dk, R) == on_tensor_cores
             ops.attention_latent(qf_t, out, gate, n, ctx, ctx.block_tables[0], plane, plane.stride(0), page, H, Dk, R, scale, window,
                                  bool(single), part=part, split_slots=slots)
+            if on_tensor_cores:          # and the CUDA-core kernel on the same rows
+                other = torch.zeros_like(out)
+                ops.attention_latent(qf_t, other, gate, n, ctx, ctx.block_tables[0], plane, plane.stride(0), page, H, Dk, R, scale,
+                                     window, bool(single), part=part, split_slots=slots, tensor_cores=False)
+                assert (other.double() - out.double()).abs().max().item() < 3e-2 * out.double().abs().max().item()
             ref = attention_rows_reference(qf_t.double().cpu().numpy(), rows, pos, H, Dk, R, scale, window, gate.double().cpu().numpy())
             got = out.double().cpu().numpy().reshape(n, H, R)
             tol = 1e-4 if dtype == "float32" else 3e-2

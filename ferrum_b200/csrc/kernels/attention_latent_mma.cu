@@ -4,10 +4,12 @@
 // first Dv), so a tile of 16 rows packs the heads of one token (or of 16 / HB tokens where the
 // model has fewer than 16 heads: HB = heads per tile, a power of two).  The output of a row
 // tile is 16 x Dv float32, too wide for one warp's registers: FOUR warps share a row tile.  For
-// a stage of 64 keys each of them forms the scores of 16 keys (Q K^T over Dk), the scores meet in
-// shared memory as float32, every warp takes the same softmax step for the tile's rows (max and sum
-// in float32 registers, identical in the four warps), rounds the weights to the 16-bit type as the A
-// operand, and multiplies them with ITS quarter of the value columns (the key rows read through
+// a stage of 64 keys each of them forms the scores of ITS 16 keys (Q K^T over Dk) and keeps them in
+// registers; the warps exchange their row maxima through shared memory, each takes the softmax
+// step for its own keys (max and sums in float32 registers; a warp's sum covers its keys, the four
+// meet once at the end), rounds its weights to the 16-bit type into a shared [16][64] operand tile,
+// and then every warp multiplies the whole tile with ITS quarter of the value columns (the key rows
+// read through
 // ldmatrix.trans).  A CTA has one row tile (steps of single tokens: 4 warps) or two (prompt
 // portions: 8 warps, twice the reuse of a key stage).  Key stages arrive by cp.async one stage
 // ahead.  Single tokens may cut their key range at multiples of 128 absolute positions among CTAs
@@ -20,7 +22,7 @@
 
 constexpr int LM_TK = 64;          // keys per stage
 constexpr int LM_SPLIT = 128;      // keys per split (the CUDA-core kernel's and the merge kernel's)
-constexpr int LM_SS = LM_TK + 4;   // row stride of the score tile (floats)
+constexpr int LM_PS = LM_TK + 8;   // row stride of the weights' operand tile (16-bit elements)
 
 __device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem, int src_bytes) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -57,8 +59,8 @@ inline LmSmem lm_smem(int Dk, int NRT) {
   LmSmem s;
   s.DKP = Dk + 8;                                    // (rows 16 bytes apart modulo 128: ldmatrix reads eight rows without bank conflicts)
   s.off_k = NRT * 16 * s.DKP * 2;
-  s.off_s = s.off_k + 2 * LM_TK * s.DKP * 2;
-  s.off_row = s.off_s + NRT * 16 * LM_SS * 4;
+  s.off_s = s.off_k + 2 * LM_TK * s.DKP * 2;                // per row tile: 64 + 64 floats (maxima, sums), then its weights tile
+  s.off_row = s.off_s + NRT * (128 * 4 + 16 * LM_PS * 2);
   s.bytes = s.off_row + 2 * LM_TK * 8;
   return s;
 }
@@ -75,7 +77,8 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
   extern __shared__ __align__(16) unsigned char lm_sm[];
   T* const sQ = reinterpret_cast<T*>(lm_sm);
   T* const sK = reinterpret_cast<T*>(lm_sm + off_k);
-  float* const sS = reinterpret_cast<float*>(lm_sm + off_s);
+  float* const sS = reinterpret_cast<float*>(lm_sm + off_s);                        // [NRT][64] maxima, [NRT][64] sums
+  T* const sP = reinterpret_cast<T*>(lm_sm + off_s + NRT * 128 * 4);                // [NRT * 16][LM_PS]
   long long* const sRow = reinterpret_cast<long long*>(lm_sm + off_row);
   __shared__ int chunk_req, chunk_t0, chunk_nt;
   constexpr int THREADS = 128 * NRT;
@@ -178,7 +181,6 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
   const int nv = Dv / 32;                       // this warp's n-tiles: value columns quarter * Dv/4 + j * 8
   const int vbase = quarter * (Dv / 4);
-  float* const sSt = sS + rt * 16 * LM_SS;
 
   for (int n = 0; n < n_tiles; ++n) {
     const int b = n & 1;
@@ -192,75 +194,88 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
     const T* const kb = sK + (size_t)b * LM_TK * DKP;
     // ---- scores of this warp's 16 keys for the row tile's 16 rows
     {
-      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+      // (two accumulator sets over alternate k-steps: four independent chains of products per warp instead of two)
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
       const T* qa = sQ + (size_t)(rt * 16 + (lane & 15)) * DKP + (lane >> 4) * 8;
       const T* kr = kb + (size_t)(quarter * 16 + (lane & 7) + ((lane >> 4) << 3)) * DKP + ((lane >> 3) & 1) * 8;
-#pragma unroll 4
-      for (int ks = 0; ks < Dk / 16; ++ks) {
-        uint32_t a[4], bq[4];
+      const int nks = Dk / 16;
+#pragma unroll 2
+      for (int ks = 0; ks + 1 < nks; ks += 2) {
+        uint32_t a[4], bq[4], a2[4], bq2[4];
         lm_ldmatrix_x4(a, qa + ks * 16);
         lm_ldmatrix_x4(bq, kr + ks * 16);
+        lm_ldmatrix_x4(a2, qa + ks * 16 + 16);
+        lm_ldmatrix_x4(bq2, kr + ks * 16 + 16);
+        lm_mma<T>(s0, a, bq[0], bq[1]);
+        lm_mma<T>(s1, a, bq[2], bq[3]);
+        lm_mma<T>(u0, a2, bq2[0], bq2[1]);
+        lm_mma<T>(u1, a2, bq2[2], bq2[3]);
+      }
+      if (nks & 1) {
+        uint32_t a[4], bq[4];
+        lm_ldmatrix_x4(a, qa + (nks - 1) * 16);
+        lm_ldmatrix_x4(bq, kr + (nks - 1) * 16);
         lm_mma<T>(s0, a, bq[0], bq[1]);
         lm_mma<T>(s1, a, bq[2], bq[3]);
       }
-      const int r0 = lane >> 2, cc = quarter * 16 + (lane & 3) * 2;
-      *reinterpret_cast<float2*>(&sSt[r0 * LM_SS + cc]) = make_float2(s0[0] * scale, s0[1] * scale);
-      *reinterpret_cast<float2*>(&sSt[(r0 + 8) * LM_SS + cc]) = make_float2(s0[2] * scale, s0[3] * scale);
-      *reinterpret_cast<float2*>(&sSt[r0 * LM_SS + cc + 8]) = make_float2(s1[0] * scale, s1[1] * scale);
-      *reinterpret_cast<float2*>(&sSt[(r0 + 8) * LM_SS + cc + 8]) = make_float2(s1[2] * scale, s1[3] * scale);
-    }
-    __syncthreads();                 // the row tile's scores are complete
-    // ---- softmax step of the thread's two rows (the same in the four warps of the row tile)
-    uint32_t pa[LM_TK / 16][4];
-    {
-      const int key0 = k_begin + n * LM_TK;
-      float sv[2][LM_TK / 16][4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s0[e] += u0[e];
+        s1[e] += u1[e];
+      }
+      // ---- this warp's share of the softmax step: its 16 keys of the thread's two rows, in registers.
+      // s0: keys cc, cc + 1 (rows r0 | r0 + 8); s1: keys cc + 8, cc + 9
+      const int key = k_begin + n * LM_TK + quarter * 16 + (lane & 3) * 2;
+      float sv[2][4];
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const float* srow = sSt + ((lane >> 2) + 8 * j) * LM_SS + (lane & 3) * 2;
+        const float vals[4] = {s0[2 * j], s0[2 * j + 1], s1[2 * j], s1[2 * j + 1]};
 #pragma unroll
-        for (int kk = 0; kk < LM_TK / 16; ++kk) {
-          const float2 u = *reinterpret_cast<const float2*>(srow + kk * 16), w = *reinterpret_cast<const float2*>(srow + kk * 16 + 8);
-          const int key = key0 + kk * 16 + (lane & 3) * 2;
-          const float vals[4] = {u.x, u.y, w.x, w.y};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int ke = key + (e & 1) + (e >> 1) * 8;
-            const bool seen = ke < k_end && ke <= r_pos[j] && ke >= r_lo[j];
-            sv[j][kk][e] = seen ? vals[e] : -INFINITY;
-            mx[j] = fmaxf(mx[j], sv[j][kk][e]);
-          }
+        for (int e = 0; e < 4; ++e) {
+          const int ke = key + (e & 1) + (e >> 1) * 8;
+          const bool seen = ke < k_end && ke <= r_pos[j] && ke >= r_lo[j];
+          sv[j][e] = seen ? vals[e] * scale : -INFINITY;
+          mx[j] = fmaxf(mx[j], sv[j][e]);
         }
         mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 1));
         mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 2));
       }
+      float* const sMx = sS + rt * 64;                       // [quarter][16 rows]: the warps' row maxima of this stage
+      if ((lane & 3) == 0) {
+        sMx[quarter * 16 + (lane >> 2)] = mx[0];
+        sMx[quarter * 16 + (lane >> 2) + 8] = mx[1];
+      }
+      __syncthreads();               // the four warps' maxima are there
       float corr[2];
+      uint32_t pw[2][2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const float m_new = fmaxf(m[j], mx[j]);
+        const int r = (lane >> 2) + 8 * j;
+        const float tile_max = fmaxf(fmaxf(sMx[r], sMx[16 + r]), fmaxf(sMx[32 + r], sMx[48 + r]));
+        const float m_new = fmaxf(m[j], tile_max);
         corr[j] = (m_new == -INFINITY || m[j] == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f) : expf(m[j] - m_new);
         float sum = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < LM_TK / 16; ++kk)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p = sv[j][kk][e] == -INFINITY ? 0.f : expf(sv[j][kk][e] - m_new);
-            sv[j][kk][e] = p;
-            sum += p;
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float p = sv[j][e] == -INFINITY ? 0.f : expf(sv[j][e] - m_new);
+          sv[j][e] = p;
+          sum += p;
+        }
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        l[j] = l[j] * corr[j] + sum;
+        l[j] = l[j] * corr[j] + sum;               // (this warp's keys only; the four warps' sums meet at the end)
         m[j] = m_new;
+        pw[j][0] = pack2<T>(sv[j][0], sv[j][1]);
+        pw[j][1] = pack2<T>(sv[j][2], sv[j][3]);
       }
-#pragma unroll
-      for (int kk = 0; kk < LM_TK / 16; ++kk) {
-        pa[kk][0] = pack2<T>(sv[0][kk][0], sv[0][kk][1]);
-        pa[kk][1] = pack2<T>(sv[1][kk][0], sv[1][kk][1]);
-        pa[kk][2] = pack2<T>(sv[0][kk][2], sv[0][kk][3]);
-        pa[kk][3] = pack2<T>(sv[1][kk][2], sv[1][kk][3]);
-      }
+      // the weights, rounded to the storage type, into the row tile's [16][LM_TK] operand tile
+      T* const sPt = sP + rt * 16 * LM_PS;
+      const int r0 = lane >> 2, cc = quarter * 16 + (lane & 3) * 2;
+      *reinterpret_cast<uint32_t*>(&sPt[r0 * LM_PS + cc]) = pw[0][0];
+      *reinterpret_cast<uint32_t*>(&sPt[r0 * LM_PS + cc + 8]) = pw[0][1];
+      *reinterpret_cast<uint32_t*>(&sPt[(r0 + 8) * LM_PS + cc]) = pw[1][0];
+      *reinterpret_cast<uint32_t*>(&sPt[(r0 + 8) * LM_PS + cc + 8]) = pw[1][1];
 #pragma unroll
       for (int j = 0; j < NV; ++j) {
         acc[j][0] *= corr[0];
@@ -269,6 +284,11 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
         acc[j][3] *= corr[1];
       }
     }
+    __syncthreads();                 // the row tile's weights are complete
+    uint32_t pa[LM_TK / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < LM_TK / 16; ++kk)
+      lm_ldmatrix_x4(pa[kk], sP + (size_t)(rt * 16 + (lane & 15)) * LM_PS + kk * 16 + (lane >> 4) * 8);
     // ---- weighted values of this warp's quarter of the columns
 #pragma unroll
     for (int kk = 0; kk < LM_TK / 16; ++kk) {
@@ -286,6 +306,21 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
   }
   lm_wait<0>();
   pdl_launch();
+  // the row sums of the four warps (each over its own keys, on the same sequence of maxima) in a fixed order
+  {
+    float* const sL = sS + NRT * 64 + rt * 64;
+    __syncthreads();
+    if ((lane & 3) == 0) {
+      sL[quarter * 16 + (lane >> 2)] = l[0];
+      sL[quarter * 16 + (lane >> 2) + 8] = l[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = (lane >> 2) + 8 * j;
+      l[j] = (sL[r] + sL[16 + r]) + (sL[32 + r] + sL[48 + r]);
+    }
+  }
 #pragma unroll
   for (int j2 = 0; j2 < 2; ++j2) {
     const int t = r_tok[j2];

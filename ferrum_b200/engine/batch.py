@@ -145,6 +145,11 @@ class StepContext:
         self._bt_host = [PinnedRing(self.max_requests * w, torch.int32, device) for w in self.table_widths]
         self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
         self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
+        # A block may run independent sublayers on a second stream (`side_stream`); products launched
+        # there take a product workspace and tile counters of their own (`lane` 1).
+        self._splitk_counters_side = torch.zeros(4096, dtype=torch.int32, device=device)
+        self.lane = 0
+        self._side = None
         self.step_cache: Dict[object, object] = {}
         self.plan_store = PlanStore(device)
         self.n_tokens = self.n_reqs = self.n_want = 0
@@ -275,6 +280,16 @@ class StepContext:
         """(float32 workspace, zeroed int32 tile counters) for the tensor-core product."""
         from ..ops import lib as ops
         floats, tiles = ops.gemm_tc_workspace(M, N, K, dual)
+        if self.lane:
+            if tiles > self._splitk_counters_side.numel():
+                self._splitk_counters_side = torch.zeros(2 * tiles, dtype=torch.int32, device=self.device)
+            return self.scratch.get("gemm_partials_side", (floats,), torch.float32), self._splitk_counters_side
         if tiles > self._splitk_counters.numel():
             self._splitk_counters = torch.zeros(2 * tiles, dtype=torch.int32, device=self.device)
         return self.scratch.get("gemm_partials", (floats,), torch.float32), self._splitk_counters
+
+    def side_stream(self):
+        """A second CUDA stream with a fork and a join event, made at first use: (stream, fork, join)."""
+        if self._side is None:
+            self._side = (torch.cuda.Stream(device=self.device), torch.cuda.Event(), torch.cuda.Event())
+        return self._side

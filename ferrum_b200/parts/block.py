@@ -32,6 +32,10 @@ class PreNormBlock(Part):
         self.ffn.forward(x, ctx, h)
 
 
+# Up to this many tokens in a step the block's second chain (gates, feed-forward) runs on a second stream.
+OVERLAP_MAX_TOKENS = 64
+
+
 class ParallelGatedBlock(Part):
     """Both sublayers read norms of the SAME residual row and their gated results are added together:
 
@@ -105,19 +109,41 @@ class ParallelGatedBlock(Part):
                             self.w_shift_weight if self.token_shift else None, a, m, b, T, ctx, state, stage, self.groups,
                             self.eps)
         y1 = ctx.buf("pgb_y1", (cap, E), torch.float32)
-        self.mixer.forward(m, ctx, cache, y1, accumulate=False)
         g1 = ctx.buf("pgb_g1", (cap, E), torch.float32)
-        linear(a, self.w_rg1_weight, g1, STORE_F32, ctx, M=T)
-        y2 = g2 = c2 = None
-        if self.ffn is not None:
-            y2 = ctx.buf("pgb_y2", (cap, E), torch.float32)
-            self.ffn.forward(b, ctx, y2, accumulate=False)
-            ctx.flush_residual()
-            c2 = getattr(self.ffn, "down_bias", None)
-            if self._rg2_fused:
-                g2 = self.ffn.extra_out
-            else:
-                g2 = ctx.buf("pgb_g2", (cap, E), torch.float32)
-                linear(b, self.w_rg2_weight, g2, STORE_F32, ctx, M=T)
+        y2 = ctx.buf("pgb_y2", (cap, E), torch.float32) if self.ffn is not None else None
+        g2 = ctx.buf("pgb_g2", (cap, E), torch.float32) if self.ffn is not None and not self._rg2_fused else None
+
+        def gates_and_ffn():
+            nonlocal g2
+            linear(a, self.w_rg1_weight, g1, STORE_F32, ctx, M=T)
+            if self.ffn is not None:
+                self.ffn.forward(b, ctx, y2, accumulate=False)
+                ctx.flush_residual()
+                if self._rg2_fused:
+                    g2 = self.ffn.extra_out
+                else:
+                    linear(b, self.w_rg2_weight, g2, STORE_F32, ctx, M=T)
+
+        # The mixer reads m; the gates and the feed-forward read a and b: two chains that meet only in
+        # the final sum.  In steps of a few tokens every kernel of a chain waits for the one before it
+        # far longer than it computes, so the second chain runs on a second stream beside the first.
+        if T <= OVERLAP_MAX_TOKENS and not ops.profiling() and str(ctx.device) != "cpu":
+            side, fork, join = ctx.side_stream()
+            main = torch.cuda.current_stream()
+            fork.record(main)
+            side.wait_event(fork)
+            ctx.lane = 1
+            try:
+                with torch.cuda.stream(side):
+                    gates_and_ffn()
+                    join.record(side)
+            finally:
+                ctx.lane = 0
+            self.mixer.forward(m, ctx, cache, y1, accumulate=False)
+            main.wait_event(join)
+        else:
+            self.mixer.forward(m, ctx, cache, y1, accumulate=False)
+            gates_and_ffn()
+        c2 = getattr(self.ffn, "down_bias", None) if self.ffn is not None else None
         ops.gated_residual(h, T, y1, g1, self.w_rg1_bias, y2, c2, g2, self.w_rg2_bias if y2 is not None else None,
                            ctx=ctx, stage=stage, state=state)

@@ -4,14 +4,14 @@
 // first Dv), so a tile of 16 rows packs the heads of one token (or of 16 / HB tokens where the
 // model has fewer than 16 heads: HB = heads per tile, a power of two).  The output of a row
 // tile is 16 x Dv float32, too wide for one warp's registers: FOUR warps share a row tile.  For
-// a stage of 64 keys each of them forms the scores of ITS 16 keys (Q K^T over Dk) and keeps them in
+// a stage of 64 or 32 keys each of them forms the scores of ITS quarter of the keys (Q K^T over Dk) and keeps them in
 // registers; the warps exchange their row maxima through shared memory, each takes the softmax
 // step for its own keys (max and sums in float32 registers; a warp's sum covers its keys, the four
 // meet once at the end), rounds its weights to the 16-bit type into a shared [16][64] operand tile,
 // and then every warp multiplies the whole tile with ITS quarter of the value columns (the key rows
 // read through
-// ldmatrix.trans).  A CTA has one row tile (steps of single tokens: 4 warps) or two (prompt
-// portions: 8 warps, twice the reuse of a key stage).  Key stages arrive by cp.async one stage
+// ldmatrix.trans).  A CTA has one row tile (steps of single tokens: 4 warps) or up to three (prompt
+// portions: 12 warps on one key stage).  Key stages arrive by cp.async one stage
 // ahead.  Single tokens may cut their key range at multiples of 128 absolute positions among CTAs
 // (partials folded by attention_latent_combine, the same as the CUDA-core kernel's).
 // Needs Dk % 16 == 0, Dv % 32 == 0, Dv <= 512 and 16-byte aligned rows; the CUDA-core kernel takes
@@ -20,9 +20,10 @@
 
 #include <type_traits>
 
-constexpr int LM_TK = 64;          // keys per stage
+// keys per stage: a template parameter TK (64: a warp forms the scores of 16 keys; 32: of 8)
 constexpr int LM_SPLIT = 128;      // keys per split (the CUDA-core kernel's and the merge kernel's)
-constexpr int LM_PS = LM_TK + 8;   // row stride of the weights' operand tile (16-bit elements)
+constexpr int LM_SMEM_LIMIT = 225 * 1024;
+// row stride of the weights' operand tile: TK + 8 16-bit elements
 
 __device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem, int src_bytes) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -55,18 +56,18 @@ __device__ __forceinline__ void lm_mma(float (&d)[4], const uint32_t (&a)[4], ui
 struct LmSmem {
   int DKP, off_k, off_s, off_row, bytes;     // offsets in bytes
 };
-inline LmSmem lm_smem(int Dk, int NRT) {
+inline LmSmem lm_smem(int Dk, int NRT, int TK) {
   LmSmem s;
   s.DKP = Dk + 8;                                    // (rows 16 bytes apart modulo 128: ldmatrix reads eight rows without bank conflicts)
   s.off_k = NRT * 16 * s.DKP * 2;
-  s.off_s = s.off_k + 2 * LM_TK * s.DKP * 2;                // per row tile: 64 + 64 floats (maxima, sums), then its weights tile
-  s.off_row = s.off_s + NRT * (128 * 4 + 16 * LM_PS * 2);
-  s.bytes = s.off_row + 2 * LM_TK * 8;
+  s.off_s = s.off_k + 2 * TK * s.DKP * 2;                // per row tile: 64 + 64 floats (maxima, sums), then its weights tile
+  s.off_row = s.off_s + NRT * (128 * 4 + 16 * (TK + 8) * 2);
+  s.bytes = s.off_row + 2 * TK * 8;
   return s;
 }
 
 // NV: n-tiles of 8 value columns per warp (Dv / 32 <= NV).  NRT: row tiles per CTA.
-template <typename T, int NV, int NRT>
+template <typename T, int NV, int NRT, int TK>
 __global__ void __launch_bounds__(128 * NRT)
 attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo, const float* __restrict__ gate,
                             const int* __restrict__ positions, const int* __restrict__ q_start, int n_reqs,
@@ -82,6 +83,9 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
   long long* const sRow = reinterpret_cast<long long*>(lm_sm + off_row);
   __shared__ int chunk_req, chunk_t0, chunk_nt;
   constexpr int THREADS = 128 * NRT;
+  constexpr int KW = TK / 4;                   // keys per warp of a stage's scores
+  constexpr int LM_PS = TK + 8;
+  static_assert(TK == 64 || TK == 32, "a stage has 64 or 32 keys");
   const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rt = wid >> 2, quarter = wid & 3;
   const int TT = 16 / HB;                       // tokens per row tile
@@ -134,12 +138,12 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
     r_lo[j] = there ? (window > 0 ? max(0, r_pos[j] - window + 1) : 0) : 0x7fffffff;
   }
   const int* bt = block_table + (size_t)req * table_width;
-  const int n_tiles = (k_end - k_begin + LM_TK - 1) / LM_TK;
-  const int chunks16 = Dk / 8;                  // 16-byte pieces of a row
+  const int n_tiles = (k_end - k_begin + TK - 1) / TK;
+  const int chunks16 = Dk / 8;                  // 16-byte pieces of a row (the queries' load)
 
   auto find_rows = [&](int n) {
-    if (threadIdx.x < LM_TK) {
-      const int key = k_begin + n * LM_TK + threadIdx.x;
+    if (threadIdx.x < TK) {
+      const int key = k_begin + n * TK + threadIdx.x;
       long long off = -1;
       if (key < k_end) {
         const int lp = key / page_size;
@@ -147,16 +151,19 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
         if (page < 0) atomicExch(err, 5);
         else off = (long long)page * page_stride + (long long)(key % page_size) * Dk;
       }
-      sRow[(n & 1) * LM_TK + threadIdx.x] = off;
+      sRow[(n & 1) * TK + threadIdx.x] = off;
     }
   };
+  // a warp per row, a lane per 16-byte piece (no index division in the loop that runs every stage)
   auto load_tile = [&](int n) {
     const int b = n & 1;
-    T* const kb = sK + (size_t)b * LM_TK * DKP;
-    for (int idx = threadIdx.x; idx < LM_TK * chunks16; idx += THREADS) {
-      const int j = idx / chunks16, d = (idx % chunks16) * 8;
-      const long long off = sRow[b * LM_TK + j];
-      lm_cp_async16(&kb[j * DKP + d], plane + (off >= 0 ? off + d : 0), off >= 0 ? 16 : 0);
+    T* const kb = sK + (size_t)b * TK * DKP;
+    for (int j = wid; j < TK; j += THREADS / 32) {
+      const long long off = sRow[b * TK + j];
+      const T* src = plane + (off >= 0 ? off : 0);
+      T* dst = kb + j * DKP;
+      const int bytes = off >= 0 ? 16 : 0;
+      for (int d = lane * 8; d < Dk; d += 256) lm_cp_async16(dst + d, src + d, bytes);
     }
   };
 
@@ -191,41 +198,62 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
     lm_commit();
     lm_wait<1>();
     __syncthreads();                 // tile n is in shared memory
-    const T* const kb = sK + (size_t)b * LM_TK * DKP;
+    const T* const kb = sK + (size_t)b * TK * DKP;
     // ---- scores of this warp's 16 keys for the row tile's 16 rows
     {
       // (two accumulator sets over alternate k-steps: four independent chains of products per warp instead of two)
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
       const T* qa = sQ + (size_t)(rt * 16 + (lane & 15)) * DKP + (lane >> 4) * 8;
-      const T* kr = kb + (size_t)(quarter * 16 + (lane & 7) + ((lane >> 4) << 3)) * DKP + ((lane >> 3) & 1) * 8;
       const int nks = Dk / 16;
+      if constexpr (KW == 16) {
+        const T* kr = kb + (size_t)(quarter * 16 + (lane & 7) + ((lane >> 4) << 3)) * DKP + ((lane >> 3) & 1) * 8;
 #pragma unroll 2
-      for (int ks = 0; ks + 1 < nks; ks += 2) {
-        uint32_t a[4], bq[4], a2[4], bq2[4];
-        lm_ldmatrix_x4(a, qa + ks * 16);
-        lm_ldmatrix_x4(bq, kr + ks * 16);
-        lm_ldmatrix_x4(a2, qa + ks * 16 + 16);
-        lm_ldmatrix_x4(bq2, kr + ks * 16 + 16);
-        lm_mma<T>(s0, a, bq[0], bq[1]);
-        lm_mma<T>(s1, a, bq[2], bq[3]);
-        lm_mma<T>(u0, a2, bq2[0], bq2[1]);
-        lm_mma<T>(u1, a2, bq2[2], bq2[3]);
-      }
-      if (nks & 1) {
-        uint32_t a[4], bq[4];
-        lm_ldmatrix_x4(a, qa + (nks - 1) * 16);
-        lm_ldmatrix_x4(bq, kr + (nks - 1) * 16);
-        lm_mma<T>(s0, a, bq[0], bq[1]);
-        lm_mma<T>(s1, a, bq[2], bq[3]);
+        for (int ks = 0; ks + 1 < nks; ks += 2) {
+          uint32_t a[4], bq[4], a2[4], bq2[4];
+          lm_ldmatrix_x4(a, qa + ks * 16);
+          lm_ldmatrix_x4(bq, kr + ks * 16);
+          lm_ldmatrix_x4(a2, qa + ks * 16 + 16);
+          lm_ldmatrix_x4(bq2, kr + ks * 16 + 16);
+          lm_mma<T>(s0, a, bq[0], bq[1]);
+          lm_mma<T>(s1, a, bq[2], bq[3]);
+          lm_mma<T>(u0, a2, bq2[0], bq2[1]);
+          lm_mma<T>(u1, a2, bq2[2], bq2[3]);
+        }
+        if (nks & 1) {
+          uint32_t a[4], bq[4];
+          lm_ldmatrix_x4(a, qa + (nks - 1) * 16);
+          lm_ldmatrix_x4(bq, kr + (nks - 1) * 16);
+          lm_mma<T>(s0, a, bq[0], bq[1]);
+          lm_mma<T>(s1, a, bq[2], bq[3]);
+        }
+      } else {
+        // eight keys per warp: one ldmatrix.x4 brings the key operands of TWO k-steps (keys x k 0-7, 8-15, 16-23, 24-31)
+        const T* kr = kb + (size_t)(quarter * 8 + (lane & 7)) * DKP + (lane >> 3) * 8;
+#pragma unroll 2
+        for (int ks = 0; ks + 1 < nks; ks += 2) {
+          uint32_t a[4], a2[4], bq[4];
+          lm_ldmatrix_x4(a, qa + ks * 16);
+          lm_ldmatrix_x4(a2, qa + ks * 16 + 16);
+          lm_ldmatrix_x4(bq, kr + ks * 16);
+          lm_mma<T>(s0, a, bq[0], bq[1]);
+          lm_mma<T>(u0, a2, bq[2], bq[3]);
+        }
+        if (nks & 1) {
+          uint32_t a[4], bq[4];
+          lm_ldmatrix_x4(a, qa + (nks - 1) * 16);
+          lm_ldmatrix_x4(bq, kr + (nks - 1) * 16 - ((lane >> 4) << 4));     // (lanes 16-31 repeat the first two pieces: stay inside the row)
+          lm_mma<T>(s0, a, bq[0], bq[1]);
+        }
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         s0[e] += u0[e];
         s1[e] += u1[e];
       }
-      // ---- this warp's share of the softmax step: its 16 keys of the thread's two rows, in registers.
-      // s0: keys cc, cc + 1 (rows r0 | r0 + 8); s1: keys cc + 8, cc + 9
-      const int key = k_begin + n * LM_TK + quarter * 16 + (lane & 3) * 2;
+      // ---- this warp's share of the softmax step: its KW keys of the thread's two rows, in registers.
+      // s0: keys cc, cc + 1 (rows r0 | r0 + 8); with 16 keys per warp s1: keys cc + 8, cc + 9
+      constexpr int NE = KW / 4;                   // score elements per thread and row
+      const int key = k_begin + n * TK + quarter * KW + (lane & 3) * 2;
       float sv[2][4];
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -234,7 +262,7 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ke = key + (e & 1) + (e >> 1) * 8;
-          const bool seen = ke < k_end && ke <= r_pos[j] && ke >= r_lo[j];
+          const bool seen = e < NE && ke < k_end && ke <= r_pos[j] && ke >= r_lo[j];
           sv[j][e] = seen ? vals[e] * scale : -INFINITY;
           mx[j] = fmaxf(mx[j], sv[j][e]);
         }
@@ -269,13 +297,15 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
         pw[j][0] = pack2<T>(sv[j][0], sv[j][1]);
         pw[j][1] = pack2<T>(sv[j][2], sv[j][3]);
       }
-      // the weights, rounded to the storage type, into the row tile's [16][LM_TK] operand tile
+      // the weights, rounded to the storage type, into the row tile's [16][TK] operand tile
       T* const sPt = sP + rt * 16 * LM_PS;
-      const int r0 = lane >> 2, cc = quarter * 16 + (lane & 3) * 2;
+      const int r0 = lane >> 2, cc = quarter * KW + (lane & 3) * 2;
       *reinterpret_cast<uint32_t*>(&sPt[r0 * LM_PS + cc]) = pw[0][0];
-      *reinterpret_cast<uint32_t*>(&sPt[r0 * LM_PS + cc + 8]) = pw[0][1];
       *reinterpret_cast<uint32_t*>(&sPt[(r0 + 8) * LM_PS + cc]) = pw[1][0];
-      *reinterpret_cast<uint32_t*>(&sPt[(r0 + 8) * LM_PS + cc + 8]) = pw[1][1];
+      if constexpr (KW == 16) {
+        *reinterpret_cast<uint32_t*>(&sPt[r0 * LM_PS + cc + 8]) = pw[0][1];
+        *reinterpret_cast<uint32_t*>(&sPt[(r0 + 8) * LM_PS + cc + 8]) = pw[1][1];
+      }
 #pragma unroll
       for (int j = 0; j < NV; ++j) {
         acc[j][0] *= corr[0];
@@ -285,13 +315,13 @@ attention_latent_mma_kernel(const T* __restrict__ q, int ldq, T* __restrict__ ou
       }
     }
     __syncthreads();                 // the row tile's weights are complete
-    uint32_t pa[LM_TK / 16][4];
+    uint32_t pa[TK / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < LM_TK / 16; ++kk)
+    for (int kk = 0; kk < TK / 16; ++kk)
       lm_ldmatrix_x4(pa[kk], sP + (size_t)(rt * 16 + (lane & 15)) * LM_PS + kk * 16 + (lane >> 4) * 8);
     // ---- weighted values of this warp's quarter of the columns
 #pragma unroll
-    for (int kk = 0; kk < LM_TK / 16; ++kk) {
+    for (int kk = 0; kk < TK / 16; ++kk) {
       const T* vr = kb + (size_t)(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * DKP + vbase + (lane >> 4) * 8;
 #pragma unroll
       for (int j = 0; j < NV; j += 2) {
@@ -359,6 +389,10 @@ FERRUM_API int ferrum_attention_latent_mma_supported(int dtype, int Dk, int Dv, 
          page_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)plane & 15) == 0 && ((uintptr_t)out & 3) == 0;
 }
 
+// For tests and measurements: 32 or 64 forces the stage size wherever it fits, 0 restores the rule.
+static int g_force_stage = 0;
+FERRUM_API void ferrum_attention_latent_mma_stage(int keys) { g_force_stage = (keys == 32 || keys == 64) ? keys : 0; }
+
 FERRUM_API int ferrum_attention_latent_mma(const void* q, int ldq, void* out, int ldo, int dtype, const float* gate, int n_tokens,
                                            const int* positions, const int* q_start, int n_reqs, const int* block_table,
                                            int table_width, const void* plane, long long page_stride, int page_size, int H, int Dk,
@@ -377,9 +411,9 @@ FERRUM_API int ferrum_attention_latent_mma(const void* q, int ldq, void* out, in
   const int TT = 16 / HB;
   const int hchunks = (H + HB - 1) / HB;
   const int nvq = Dv / 32;
-#define LM_LAUNCH(NV_, NRT_)                                                                                                 \
+#define LM_LAUNCH(NV_, NRT_, TK_)                                                                                              \
   do {                                                                                                                       \
-    const LmSmem s = lm_smem(Dk, NRT_);                                                                                      \
+    const LmSmem s = lm_smem(Dk, NRT_, TK_);                                                                                   \
     const int TQ_ = TT * NRT_;                                                                                               \
     const long long chunks = TQ_ == 1 ? n_tokens : (n_tokens + TQ_ - 1) / TQ_ + n_reqs;                                      \
     const long long ctas = chunks * hchunks;                                                                                 \
@@ -387,22 +421,42 @@ FERRUM_API int ferrum_attention_latent_mma(const void* q, int ldq, void* out, in
     FERRUM_DISPATCH_16BIT(dtype, T, {                                                                                        \
       static int configured = 0;                                                                                             \
       if (configured < s.bytes) {                                                                                            \
-        cudaError_t e = cudaFuncSetAttribute(attention_latent_mma_kernel<T, NV_, NRT_>,                                      \
+        cudaError_t e = cudaFuncSetAttribute(attention_latent_mma_kernel<T, NV_, NRT_, TK_>,                                      \
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, s.bytes);                          \
         FERRUM_CHECK_ARG(e == cudaSuccess, "latent attention: cannot reserve %d bytes of shared memory: %s", s.bytes,        \
                          cudaGetErrorString(e));                                                                             \
         configured = s.bytes;                                                                                                \
       }                                                                                                                      \
-      launch_kernel(attention_latent_mma_kernel<T, NV_, NRT_>, dim3((unsigned)ctas, part ? split_slots : 1), dim3(128 * NRT_), \
+      launch_kernel(attention_latent_mma_kernel<T, NV_, NRT_, TK_>, dim3((unsigned)ctas, part ? split_slots : 1), dim3(128 * NRT_), \
                     (size_t)s.bytes, stream, (const T*)q, ldq, (T*)out, ldo, gate, positions, q_start, n_reqs, block_table,    \
                     table_width, (const T*)plane, page_stride, page_size, H, HB, Dk, Dv, scale, window, err_flag, s.DKP,       \
                     s.off_k, s.off_s, s.off_row, part, split_slots);                                                          \
     });                                                                                                                      \
   } while (0)
-#define LM_SHAPES(NV_)                          \
-  do {                                          \
-    if (single_tokens) LM_LAUNCH(NV_, 1);       \
-    else LM_LAUNCH(NV_, 2);                     \
+  // Prompt portions: three row tiles (12 warps) on stages of 64 keys where shared memory holds them, else
+  // two, else (a very long key row) two on stages of 32 keys.  Single tokens: one row tile; stages of 32
+  // keys let two CTAs share an SM, which pays once the grid has more than two CTAs per SM; a
+  // smaller grid runs stages of 64 keys (fewer barriers per key).  (Measured at 16 heads, rows of
+  // 576: prompt of 2,048 tokens 559 us against 684 us with four row tiles on stages of 32 keys; 8
+  // single tokens over 8,192 keys 71 against 88 us, over 2,048 keys 32 against 26 us.)
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  bool big_grid = (long long)n_tokens * hchunks * (part ? split_slots : 1) > 2LL * sms;
+  int fit64 = lm_smem(Dk, 3, 64).bytes <= LM_SMEM_LIMIT ? 3 : (lm_smem(Dk, 2, 64).bytes <= LM_SMEM_LIMIT ? 2 : 0);
+  if (g_force_stage == 32) big_grid = true, fit64 = 0;
+  if (g_force_stage == 64) big_grid = false;
+#define LM_SHAPES(NV_)                                                          \
+  do {                                                                          \
+    if (single_tokens) {                                                        \
+      if (big_grid || lm_smem(Dk, 1, 64).bytes > LM_SMEM_LIMIT) LM_LAUNCH(NV_, 1, 32); \
+      else LM_LAUNCH(NV_, 1, 64);                                               \
+    } else if (fit64 == 3) LM_LAUNCH(NV_, 3, 64);                               \
+    else if (fit64 == 2) LM_LAUNCH(NV_, 2, 64);                                 \
+    else LM_LAUNCH(NV_, 2, 32);                                                 \
   } while (0)
   if (nvq <= 4) LM_SHAPES(4);
   else if (nvq <= 8) LM_SHAPES(8);

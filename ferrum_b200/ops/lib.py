@@ -668,6 +668,12 @@ def attention_latent(qf, out, gate, n_tokens, ctx, block_table, plane, page_stri
         globals()["launches"] += 1        # (the merge of the splits is a second kernel)
 
 
+def attention_latent_mma_stage(keys=0):
+    """For tests and measurements: force the tensor-core kernel's stage size (32 or 64 keys) wherever it
+    fits; 0 restores its own rule (attention_latent_mma.cu)."""
+    lib().ferrum_attention_latent_mma_stage(c_int(int(keys)))
+
+
 def attention_latent_mma_supported(qf, out, plane, page_stride, Dk, Dv):
     """True where the tensor-core kernel (attention_latent_mma.cu) takes the shape and the pointers."""
     return qf.dtype in SIXTEEN_BIT and bool(lib().ferrum_attention_latent_mma_supported(

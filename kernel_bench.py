@@ -38,6 +38,7 @@ def main():
     ap.add_argument("--kv-rank", type=int, default=512, help="latent_*: elements of the cached latent (the values)")
     ap.add_argument("--rot-dim", type=int, default=64, help="latent_*: rotated key elements behind the latent")
     ap.add_argument("--window", type=int, default=0, help="latent_*: keys a query looks back over (0: all)")
+    ap.add_argument("--stage", type=int, default=0, choices=[0, 32, 64], help="latent_*: force the tensor-core kernel's stage size")
     ap.add_argument("--cuda-cores", action="store_true", help="latent_*: the CUDA-core kernel also where the tensor-core one applies")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -120,6 +121,7 @@ def main():
     elif args.kernel in ("latent_decode", "latent_prefill"):
         # attention over cached rows of kv_rank + rot_dim elements, --hq heads sharing them
         decode = args.kernel == "latent_decode"
+        ops.attention_latent_mma_stage(args.stage)
         R = args.batch if decode else 1
         qlen = 1 if decode else args.tokens
         ctx_len = args.context if decode else args.tokens

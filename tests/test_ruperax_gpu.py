@@ -223,11 +223,17 @@ def test_attention_over_cached_rows_sees_exactly_its_window(cuda, dtype, H, R, R
             assert ops.attention_latent_mma_supported(qf_t, out, plane, plane.stride(0), Dk, R) == on_tensor_cores
             ops.attention_latent(qf_t, out, gate, n, ctx, ctx.block_tables[0], plane, plane.stride(0), page, H, Dk, R, scale, window,
                                  bool(single), part=part, split_slots=slots)
-            if on_tensor_cores:          # and the CUDA-core kernel on the same rows
-                other = torch.zeros_like(out)
-                ops.attention_latent(qf_t, other, gate, n, ctx, ctx.block_tables[0], plane, plane.stride(0), page, H, Dk, R, scale,
-                                     window, bool(single), part=part, split_slots=slots, tensor_cores=False)
-                assert (other.double() - out.double()).abs().max().item() < 3e-2 * out.double().abs().max().item()
+            if on_tensor_cores:          # the other stage size of the kernel, and the CUDA-core kernel, on the same rows
+                for stage in (32, 64, None):
+                    other = torch.zeros_like(out)
+                    ops.attention_latent_mma_stage(stage or 0)
+                    try:
+                        ops.attention_latent(qf_t, other, gate, n, ctx, ctx.block_tables[0], plane, plane.stride(0), page, H, Dk, R,
+                                             scale, window, bool(single), part=part, split_slots=slots,
+                                             tensor_cores=None if stage else False)
+                    finally:
+                        ops.attention_latent_mma_stage(0)
+                    assert (other.double() - out.double()).abs().max().item() < 3e-2 * out.double().abs().max().item(), stage
             ref = attention_rows_reference(qf_t.double().cpu().numpy(), rows, pos, H, Dk, R, scale, window, gate.double().cpu().numpy())
             got = out.double().cpu().numpy().reshape(n, H, R)
             tol = 1e-4 if dtype == "float32" else 3e-2

@@ -17,7 +17,7 @@
 #include "common.cuh"
 
 constexpr int GB_THREADS = 256;
-constexpr int GB_MAX_GROUPS = 64;
+constexpr int GB_MAX_GROUPS = 512;
 
 // 1 / sqrt(mean(part^2) + eps) of every group of row xr into inv[0 .. groups): warp w takes groups
 // w, w + warps, ...; a lane walks its group with stride 32, then the lanes meet in a butterfly.

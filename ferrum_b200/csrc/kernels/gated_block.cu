@@ -15,6 +15,7 @@
 // copied into the state by the block's last kernel: the state is read and written by different
 // launches, never by blocks of one grid.
 #include "common.cuh"
+#include "partials.cuh"
 
 constexpr int GB_THREADS = 256;
 constexpr int GB_MAX_GROUPS = 512;
@@ -200,9 +201,49 @@ FERRUM_API int ferrum_bias_glu(const float* gu, int ld, const float* bias_gate, 
   return 0;
 }
 
+// The same from a product still in partials (deferred mode): one product of 2F + n_extra rows
+// (gate | up | extra); the extra columns (another product of the same input) are summed into
+// extra[t, :] (float32) on the way.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+bias_glu_reduce_kernel(const float* __restrict__ bg, const float* __restrict__ bu, TOut* __restrict__ act, int ld_out, int F, int kind,
+                       float* __restrict__ extra, int n_extra, const PartialLayout L) {
+  __shared__ PartialTable tab;
+  build_partial_table(L, tab);
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.y;
+  for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F + n_extra; f += gridDim.x * blockDim.x) {
+    if (f < F) {
+      const float g = partial_sum(L, tab, t, f) + (bg ? bg[f] : 0.f), u = partial_sum(L, tab, t, F + f) + (bu ? bu[f] : 0.f);
+      act[(size_t)t * ld_out + f] = from_f32<TOut>(glu_act(g, kind) * u);
+    } else {
+      extra[(size_t)t * n_extra + (f - F)] = partial_sum(L, tab, t, 2 * F + (f - F));
+    }
+  }
+}
+
+FERRUM_API int ferrum_bias_glu_reduce(const float* bias_gate, const float* bias_up, void* act, int act_dtype, int ld_out, int n_tokens,
+                                      int F, int kind, float* extra, int n_extra, const float* partials, const int* layout,
+                                      cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && n_tokens <= 65535 && F > 0 && ld_out >= F && n_extra >= 0, "bias glu: bad sizes T=%d F=%d", n_tokens, F);
+  FERRUM_CHECK_ARG(kind == 0 || kind == 1, "bias glu: unknown activation %d", kind);
+  FERRUM_CHECK_ARG(n_extra == 0 || extra != nullptr, "bias glu: the extra columns need a place");
+  if (n_tokens == 0) return 0;
+  PartialLayout L;
+  if (int r = partial_make_layout(partials, layout, &L)) return r;
+  FERRUM_CHECK_ARG(2 * F + n_extra <= L.tiles * 128 && n_tokens <= L.acc_cols, "bias glu: the partials do not cover the rows");
+  const dim3 grid(min((F + n_extra + 255) / 256, 64), n_tokens);
+  FERRUM_DISPATCH_DTYPE(act_dtype, T, launch_kernel(bias_glu_reduce_kernel<T>, grid, dim3(256), 0, stream, bias_gate, bias_up, (T*)act, ld_out, F,
+                                                    kind, extra, n_extra, L));
+  FERRUM_CHECK_LAUNCH("bias_glu_reduce");
+  return 0;
+}
+
 // ---------------------------------------------------------------- gated residual sum
 // x[t, i] += y1[t, i] * sigmoid(g1[t, i] + c1[i]) + (y2[t, i] + c2[i]) * sigmoid(g2[t, i] + c3[i]); the second term is
-// left out when y2 is null.  All float32; every operand has its own row stride.  The block of a
+// left out when y2 is null.  All float32; every operand has its own row stride.  y1 and y2 may each be a
+// product still in partials (deferred mode), summed while it is read.  The block of a
 // portion's last token also copies the staged row of its request into the state.
 __device__ __forceinline__ float gb_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
@@ -211,15 +252,25 @@ gated_residual_kernel(float* __restrict__ x, int E, const float* __restrict__ y1
                       const float* __restrict__ c1, const float* __restrict__ y2, int ld_y2, const float* __restrict__ c2,
                       const float* __restrict__ g2, int ld_g2, const float* __restrict__ c3, const int* __restrict__ req_of_token,
                       const int* __restrict__ q_start, const int* __restrict__ slots, const float* __restrict__ stage,
-                      float* __restrict__ state) {
+                      float* __restrict__ state, const PartialLayout L1, const PartialLayout L2) {
+  __shared__ PartialTable tab1, tab2;
+  if (L1.ws != nullptr) build_partial_table(L1, tab1);
+  if (L2.ws != nullptr) build_partial_table(L2, tab2);
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * E;
-  for (int i = threadIdx.x; i < E; i += blockDim.x) {
-    float add = y1[(size_t)t * ld_y1 + i] * gb_sigmoid(g1[(size_t)t * ld_g1 + i] + (c1 ? c1[i] : 0.f));
-    if (y2 != nullptr)
-      add += (y2[(size_t)t * ld_y2 + i] + (c2 ? c2[i] : 0.f)) * gb_sigmoid(g2[(size_t)t * ld_g2 + i] + (c3 ? c3[i] : 0.f));
+  const bool second = y2 != nullptr || L2.ws != nullptr;
+  // (with few tokens a row is shared out between gridDim.y blocks: summing partials is several loads per element)
+  const int per = (E + gridDim.y - 1) / gridDim.y;
+  const int lo = blockIdx.y * per, hi = min(E, lo + per);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v1 = L1.ws != nullptr ? partial_sum(L1, tab1, t, i) : y1[(size_t)t * ld_y1 + i];
+    float add = v1 * gb_sigmoid(g1[(size_t)t * ld_g1 + i] + (c1 ? c1[i] : 0.f));
+    if (second) {
+      const float v2 = L2.ws != nullptr ? partial_sum(L2, tab2, t, i) : y2[(size_t)t * ld_y2 + i];
+      add += (v2 + (c2 ? c2[i] : 0.f)) * gb_sigmoid(g2[(size_t)t * ld_g2 + i] + (c3 ? c3[i] : 0.f));
+    }
     xr[i] += add;
   }
   if (state != nullptr) {
@@ -227,7 +278,7 @@ gated_residual_kernel(float* __restrict__ x, int E, const float* __restrict__ y1
     if (t == q_start[r + 1] - 1) {
       float* dst = state + (size_t)slots[r] * E;
       const float* src = stage + (size_t)r * E;
-      for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = src[i];
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
     }
   }
 }
@@ -235,14 +286,25 @@ gated_residual_kernel(float* __restrict__ x, int E, const float* __restrict__ y1
 FERRUM_API int ferrum_gated_residual(float* x, int n_tokens, int E, const float* y1, int ld_y1, const float* g1, int ld_g1,
                                      const float* c1, const float* y2, int ld_y2, const float* c2, const float* g2, int ld_g2,
                                      const float* c3, const int* req_of_token, const int* q_start, const int* slots,
-                                     const float* stage, float* state, cudaStream_t stream) {
-  FERRUM_CHECK_ARG(n_tokens >= 0 && E > 0 && y1 != nullptr && g1 != nullptr, "gated residual: bad arguments");
-  FERRUM_CHECK_ARG(y2 == nullptr || g2 != nullptr, "gated residual: the second term needs its gate");
+                                     const float* stage, float* state, const float* partials1, const int* layout1,
+                                     const float* partials2, const int* layout2, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && E > 0 && (y1 != nullptr || partials1 != nullptr) && g1 != nullptr, "gated residual: bad arguments");
+  FERRUM_CHECK_ARG((y2 == nullptr && partials2 == nullptr) || g2 != nullptr, "gated residual: the second term needs its gate");
+  PartialLayout L1{nullptr, 0, 0, 0, 0}, L2{nullptr, 0, 0, 0, 0};
+  if (partials1 != nullptr) {
+    if (int r = partial_make_layout(partials1, layout1, &L1)) return r;
+    FERRUM_CHECK_ARG(E <= L1.tiles * 128 && n_tokens <= L1.acc_cols, "gated residual: the partials do not cover the rows");
+  }
+  if (partials2 != nullptr) {
+    if (int r = partial_make_layout(partials2, layout2, &L2)) return r;
+    FERRUM_CHECK_ARG(E <= L2.tiles * 128 && n_tokens <= L2.acc_cols, "gated residual: the partials do not cover the rows");
+  }
   FERRUM_CHECK_ARG(state == nullptr || (stage != nullptr && slots != nullptr && q_start != nullptr && req_of_token != nullptr),
                    "gated residual: the state copy needs the batch description");
   if (n_tokens == 0) return 0;
-  launch_kernel(gated_residual_kernel, n_tokens, GB_THREADS, 0, stream, x, E, y1, ld_y1, g1, ld_g1, c1, y2, ld_y2, c2, g2, ld_g2, c3,
-                req_of_token, q_start, slots, stage, state);
+  const int slices = n_tokens <= 64 ? max(1, min(16, E / 256)) : 1;
+  launch_kernel(gated_residual_kernel, dim3(n_tokens, slices), dim3(GB_THREADS), 0, stream, x, E, y1, ld_y1, g1, ld_g1, c1, y2, ld_y2, c2, g2, ld_g2, c3,
+                req_of_token, q_start, slots, stage, state, L1, L2);
   FERRUM_CHECK_LAUNCH("gated_residual");
   return 0;
 }

@@ -12,6 +12,7 @@
 // latent_q_rope: the rotated part of every query head, moved behind the folded part.
 // attention_latent: the attention itself, float32 arithmetic, for float32 and 16-bit storage.
 #include "common.cuh"
+#include "partials.cuh"
 
 constexpr int LAT_THREADS = 256;
 
@@ -30,12 +31,19 @@ latent_prep_kernel(const float* __restrict__ proj, int ld, int off_q, int q_rank
                    int rot_dim, const float* __restrict__ wkv, int off_gate, int n_gate, const int* __restrict__ positions,
                    const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_width,
                    const float* __restrict__ cos_sin, int n_pos, int rope_dims, T* __restrict__ plane, long long page_stride,
-                   int page_size, T* __restrict__ cq, int ld_cq, float* __restrict__ gate, float eps, int* __restrict__ err) {
+                   int page_size, T* __restrict__ cq, int ld_cq, float* __restrict__ gate, float eps, int* __restrict__ err,
+                   int n_in, const PartialLayout L) {
   __shared__ float red[32];
+  __shared__ PartialTable tab;
+  extern __shared__ __align__(16) float lp_row[];      // the token's n_in projections
+  if (L.ws != nullptr) build_partial_table(L, tab);
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
-  const float* row = proj + (size_t)t * ld;
+  // the row once into shared memory: from the product's output, or summed from its partials
+  for (int i = threadIdx.x; i < n_in; i += blockDim.x) lp_row[i] = L.ws != nullptr ? partial_sum(L, tab, t, i) : proj[(size_t)t * ld + i];
+  __syncthreads();
+  const float* row = lp_row;
   if (q_rank > 0) {
     const float* p = row + off_q;
     float ss = 0.f;
@@ -70,6 +78,8 @@ latent_prep_kernel(const float* __restrict__ proj, int ld, int off_q, int q_rank
     dst[kv_rank + i] = from_f32<T>(rope_dims > 0 ? latent_rotated(p + kv_rank, i, rope_dims, cs) : p[kv_rank + i]);
 }
 
+// With `partials` (a product left in deferred mode, see partials.cuh) the projections are summed from
+// them instead of read from proj.
 // proj: [T, ld] float32 rows holding the query down-projection at off_q (q_rank elements; 0: none),
 // the key/value down-projection at off_kv (kv_rank + rot_dim elements; off_kv < 0: this layer
 // writes no cache) and n_gate gate logits at off_gate.  A cache page holds page_size rows of
@@ -78,16 +88,31 @@ FERRUM_API int ferrum_latent_prep(const float* proj, int ld, int n_tokens, int o
                                   int kv_rank, int rot_dim, const float* wkv, int off_gate, int n_gate, const int* positions,
                                   const int* req_of_token, const int* block_table, int table_width, const float* cos_sin,
                                   int n_pos, int rope_dims, void* plane, long long page_stride, int page_size, void* cq,
-                                  int ld_cq, int dtype, float* gate, float eps, int* err_flag, cudaStream_t stream) {
+                                  int ld_cq, int dtype, float* gate, float eps, int* err_flag, const float* partials,
+                                  const int* layout, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && q_rank >= 0 && kv_rank > 0 && rot_dim >= 0 && n_gate >= 0, "latent prep: bad sizes");
+  int n_in = off_q + q_rank;
+  if (off_kv >= 0 && off_kv + kv_rank + rot_dim > n_in) n_in = off_kv + kv_rank + rot_dim;
+  if (off_gate + n_gate > n_in) n_in = off_gate + n_gate;
+  FERRUM_CHECK_ARG(n_in * 4 <= 200 * 1024 && (partials != nullptr || (proj != nullptr && ld >= n_in)), "latent prep: %d projections a token", n_in);
+  PartialLayout L{nullptr, 0, 0, 0, 0};
+  if (partials != nullptr) {
+    if (int r = partial_make_layout(partials, layout, &L)) return r;
+    FERRUM_CHECK_ARG(n_in <= L.tiles * 128 && n_tokens <= L.acc_cols, "latent prep: the partials do not cover the rows");
+  }
   FERRUM_CHECK_ARG(rope_dims >= 0 && rope_dims % 2 == 0 && rope_dims <= rot_dim, "latent prep: %d rotated dimensions of %d", rope_dims, rot_dim);
   FERRUM_CHECK_ARG(off_kv < 0 || (plane != nullptr && page_size > 0 && table_width > 0), "latent prep: cache arguments missing");
   FERRUM_CHECK_ARG(eps > 0.f, "latent prep: eps must be positive");
   if (n_tokens == 0) return 0;
-  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(latent_prep_kernel<T>, n_tokens, LAT_THREADS, 0, stream, proj, ld, off_q, q_rank, wq, off_kv,
-                                                kv_rank, rot_dim, wkv, off_gate, n_gate, positions, req_of_token, block_table, table_width,
-                                                cos_sin, n_pos, rope_dims, (T*)plane, page_stride, page_size, (T*)cq, ld_cq, gate, eps,
-                                                err_flag));
+  FERRUM_DISPATCH_DTYPE(dtype, T, {
+    if (n_in * 4 > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(latent_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, n_in * 4);
+      FERRUM_CHECK_ARG(e == cudaSuccess, "latent prep: cannot reserve %d bytes of shared memory: %s", n_in * 4, cudaGetErrorString(e));
+    }
+    launch_kernel(latent_prep_kernel<T>, n_tokens, LAT_THREADS, (size_t)n_in * 4, stream, proj, ld, off_q, q_rank, wq, off_kv, kv_rank,
+                  rot_dim, wkv, off_gate, n_gate, positions, req_of_token, block_table, table_width, cos_sin, n_pos, rope_dims,
+                  (T*)plane, page_stride, page_size, (T*)cq, ld_cq, gate, eps, err_flag, n_in, L);
+  });
   FERRUM_CHECK_LAUNCH("latent_prep");
   return 0;
 }

@@ -57,3 +57,19 @@ __device__ __forceinline__ float partial_sum(const PartialLayout& L, const Parti
   for (int s = 0; s < PARTIAL_MAX_CONTRIB; ++s) acc += v[s];
   return acc;
 }
+
+// The four numbers a product in deferred mode hands to its consumer (k-blocks per tile, tiles,
+// CTAs, columns per partial) as a PartialLayout; returns non-zero (and sets the error text) when
+// they cannot be what the product kernel writes.
+static inline int partial_make_layout(const float* ws, const int* layout, PartialLayout* L) {
+  FERRUM_CHECK_ARG(ws && layout && layout[0] > 0 && layout[1] > 0 && layout[2] > 0 && layout[3] > 0, "partials: bad layout");
+  FERRUM_CHECK_ARG(layout[1] <= PARTIAL_MAX_TILES && layout[2] < 65536, "partials: more than %d tiles", PARTIAL_MAX_TILES);
+  const long long per = (long long)layout[0] * layout[1] / layout[2];
+  FERRUM_CHECK_ARG(per > 0 && layout[0] / per + 2 <= PARTIAL_MAX_CONTRIB, "partials: too many CTAs share a tile");
+  L->ws = ws;
+  L->nkb = layout[0];
+  L->tiles = layout[1];
+  L->n_ctas = layout[2];
+  L->acc_cols = layout[3];
+  return 0;
+}

@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 8
+ABI = 9
 
 
 def lib():
@@ -570,10 +570,27 @@ def bias_glu(gu, bias_gate, bias_up, act, n_tokens, F, kind="silu"):
                                  c_int(act.stride(0)), c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), _stream()), "bias_glu")
 
 
-def gated_residual(x, n_tokens, y1, g1, c1, y2=None, c2=None, g2=None, c3=None, ctx=None, stage=None, state=None):
+def bias_glu_reduce(partials, bias_gate, bias_up, act, n_tokens, F, kind="silu", extra=None):
+    """`bias_glu` on a product of 2F + n rows (gate | up | extra) that was left in deferred mode; the n
+    extra columns are summed into `extra` (float32 [T, n], contiguous)."""
+    _need(act, None, "act", 2)
+    n_extra = 0
+    if extra is not None:
+        _need(extra, torch.float32, "extra", 2)
+        if not extra.is_contiguous():
+            raise KernelError("bias_glu_reduce: extra must be contiguous")
+        n_extra = extra.shape[1]
+    _check(lib().ferrum_bias_glu_reduce(_ptr(bias_gate), _ptr(bias_up), _ptr(act), dtype_code(act.dtype), c_int(act.stride(0)),
+                                        c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), _ptr(extra), c_int(n_extra),
+                                        _ptr(partials.workspace), partials._c, _stream()), "bias_glu_reduce")
+
+
+def gated_residual(x, n_tokens, y1, g1, c1, y2=None, c2=None, g2=None, c3=None, ctx=None, stage=None, state=None, p1=None,
+                   p2=None):
     """x += y1 * sigmoid(g1 + c1) + (y2 + c2) * sigmoid(g2 + c3), all float32 (the second term only with
-    y2).  With `state` the staged row of every request whose portion ends in this batch is copied
-    into its state row."""
+    y2 or p2).  p1 / p2: y1 / y2 as a product left in deferred mode (`Partials`), summed while read.
+    With `state` the staged row of every request whose portion ends in this batch is copied into its
+    state row."""
     _need(x, torch.float32, "x", 2)
     for t in (y1, g1, y2, g2):
         if t is not None:
@@ -586,30 +603,37 @@ def gated_residual(x, n_tokens, y1, g1, c1, y2=None, c2=None, g2=None, c3=None, 
                                        _ptr(y2), ld(y2), _ptr(c2), _ptr(g2), ld(g2), _ptr(c3),
                                        _ptr(ctx.req_of_token if state is not None else None),
                                        _ptr(ctx.q_start if state is not None else None),
-                                       _ptr(ctx.slots if state is not None else None), _ptr(stage), _ptr(state), _stream()),
-           "gated_residual")
+                                       _ptr(ctx.slots if state is not None else None), _ptr(stage), _ptr(state),
+                                       _ptr(p1.workspace if p1 is not None else None), p1._c if p1 is not None else None,
+                                       _ptr(p2.workspace if p2 is not None else None), p2._c if p2 is not None else None,
+                                       _stream()), "gated_residual")
 
 
 # ----------------------------------------------------------------------------- attention over a cached latent
 def latent_prep(proj, n_tokens, off_q, q_rank, wq, off_kv, kv_rank, rot_dim, wkv, off_gate, n_gate, ctx, block_table, rot,
-                plane, page_stride, page_size, cq, gate, eps):
+                plane, page_stride, page_size, cq, gate, eps, partials=None):
     """From a token's float32 down-projections: the normalised query latent `cq`, the cache row
     (normalised latent, rotated key part) at the token's page (off_kv < 0: no cache write) and the
-    sigmoid of the gate logits (latent.cu)."""
-    _need(proj, torch.float32, "proj", 2); _need(cq, None, "cq", 2); _need(gate, torch.float32, "gate", 2)
+    sigmoid of the gate logits (latent.cu).  With `partials` (the product left in deferred mode) the
+    projections are summed from them and `proj` may be None."""
+    if partials is None:
+        _need(proj, torch.float32, "proj", 2)
+    _need(cq, None, "cq", 2); _need(gate, torch.float32, "gate", 2)
     if off_kv >= 0:
         _need(plane, cq.dtype, "plane")
     cos_sin = rot.cos_sin if rot is not None else None
     global _work
     if _profile is not None:
-        _work = (n_tokens * (proj.shape[1] * 4 + (q_rank + (kv_rank + rot_dim if off_kv >= 0 else 0)) * cq.element_size()), 0.0)
-    _check(lib().ferrum_latent_prep(_ptr(proj), c_int(proj.stride(0)), c_int(n_tokens), c_int(off_q), c_int(q_rank), _ptr(wq),
+        _work = (n_tokens * ((off_gate + n_gate) * 4 + (q_rank + (kv_rank + rot_dim if off_kv >= 0 else 0)) * cq.element_size()), 0.0)
+    _check(lib().ferrum_latent_prep(_ptr(proj), c_int(proj.stride(0) if proj is not None else 0), c_int(n_tokens), c_int(off_q), c_int(q_rank), _ptr(wq),
                                     c_int(off_kv), c_int(kv_rank), c_int(rot_dim), _ptr(wkv), c_int(off_gate), c_int(n_gate),
                                     _ptr(ctx.positions), _ptr(ctx.req_of_token), _ptr(block_table), c_int(block_table.shape[1]),
                                     _ptr(cos_sin), c_int(cos_sin.shape[0] if rot is not None else 0),
                                     c_int(rot.rope_dim if rot is not None else 0), _ptr(plane if off_kv >= 0 else None),
                                     c_longlong(page_stride), c_int(page_size), _ptr(cq), c_int(cq.stride(0)),
-                                    dtype_code(cq.dtype), _ptr(gate), c_float(eps), _ptr(ctx.err), _stream()), "latent_prep")
+                                    dtype_code(cq.dtype), _ptr(gate), c_float(eps), _ptr(ctx.err),
+                                    _ptr(partials.workspace if partials is not None else None),
+                                    partials._c if partials is not None else None, _stream()), "latent_prep")
 
 
 def latent_q_rope(q, qf, n_tokens, positions, rot, H, Dn, Rr, R, err):

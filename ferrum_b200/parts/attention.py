@@ -62,7 +62,7 @@ class PagedAttention(Mixer):
     def cache_need(self):
         return CacheNeed(paged=PagedKVNeed(self.Hkv, self.D, self.window))
 
-    def forward(self, x, ctx, cache, residual, accumulate=True):
+    def forward(self, x, ctx, cache, residual, accumulate=True, defer=False):
         T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
         qw = Hq * D
         qkv = ctx.buf("attn_qkv", (ctx.token_capacity, (Hq + 2 * Hkv) * D), self.dtype)

@@ -128,12 +128,15 @@ class Mixer(Part):
         and while `ctx.fixed_shapes` is set make grid sizes depend on the batch's sizes only."""
         return None
 
-    def forward(self, x, ctx, cache, residual, accumulate=True) -> None:
+    def forward(self, x, ctx, cache, residual, accumulate=True, defer=False):
         """accumulate=False: `residual` is a float32 buffer of the block's own that receives the
-        mixer's output instead of having it added (a block that scales it before the sum)."""
+        mixer's output instead of having it added (a block that scales it before the sum).  With
+        defer=True as well the part MAY leave its last product in deferred mode and return the
+        `ops.Partials` (nothing is written to `residual` then; the caller's next kernel sums them
+        before another product runs on the same lane); it returns None when it wrote `residual`."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, x, ctx, residual, accumulate=True) -> None:
+    def forward(self, x, ctx, residual, accumulate=True, defer=False):
         raise NotImplementedError

@@ -113,16 +113,19 @@ class ParallelGatedBlock(Part):
         y2 = ctx.buf("pgb_y2", (cap, E), torch.float32) if self.ffn is not None else None
         g2 = ctx.buf("pgb_g2", (cap, E), torch.float32) if self.ffn is not None and not self._rg2_fused else None
 
-        def gates_and_ffn():
-            nonlocal g2
+        p1 = p2 = None
+
+        def gates_and_ffn(defer):
+            """The second chain; the feed-forward's last product may stay in partials (`defer`), so it runs last."""
+            nonlocal g2, p2
             linear(a, self.w_rg1_weight, g1, STORE_F32, ctx, M=T)
             if self.ffn is not None:
-                self.ffn.forward(b, ctx, y2, accumulate=False)
+                if not self._rg2_fused:
+                    linear(b, self.w_rg2_weight, g2, STORE_F32, ctx, M=T)
+                p2 = self.ffn.forward(b, ctx, y2, accumulate=False, defer=defer)
                 ctx.flush_residual()
                 if self._rg2_fused:
                     g2 = self.ffn.extra_out
-                else:
-                    linear(b, self.w_rg2_weight, g2, STORE_F32, ctx, M=T)
 
         # The mixer reads m; the gates and the feed-forward read a and b: two chains that meet only in
         # the final sum.  In steps of a few tokens every kernel of a chain waits for the one before it
@@ -135,15 +138,17 @@ class ParallelGatedBlock(Part):
             ctx.lane = 1
             try:
                 with torch.cuda.stream(side):
-                    gates_and_ffn()
+                    gates_and_ffn(True)
                     join.record(side)
             finally:
                 ctx.lane = 0
-            self.mixer.forward(m, ctx, cache, y1, accumulate=False)
+            # (each chain's last product may stay in partials of its own lane's workspace: the final kernel sums both)
+            p1 = self.mixer.forward(m, ctx, cache, y1, accumulate=False, defer=True)
             main.wait_event(join)
         else:
             self.mixer.forward(m, ctx, cache, y1, accumulate=False)
-            gates_and_ffn()
+            gates_and_ffn(False)
         c2 = getattr(self.ffn, "down_bias", None) if self.ffn is not None else None
-        ops.gated_residual(h, T, y1, g1, self.w_rg1_bias, y2, c2, g2, self.w_rg2_bias if y2 is not None else None,
-                           ctx=ctx, stage=stage, state=state)
+        ops.gated_residual(h, T, y1 if p1 is None else None, g1, self.w_rg1_bias, y2 if p2 is None else None, c2, g2,
+                           self.w_rg2_bias if y2 is not None else None,
+                           ctx=ctx, stage=stage, state=state, p1=p1, p2=p2)

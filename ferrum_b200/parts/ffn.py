@@ -19,7 +19,7 @@ import torch
 
 from ..ops import lib as ops
 from .base import FeedForward, ParamSpec
-from .linear import RESIDUAL, STORE, STORE_F32, linear, linear_swiglu
+from .linear import RESIDUAL, STORE, STORE_F32, linear, linear_deferred, linear_swiglu
 
 
 class SwiGLU(FeedForward):
@@ -60,17 +60,27 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat(rows, dim=0).contiguous()
         self.w_gate_weight = self.w_up_weight = self.extra_rows = None
 
-    def forward(self, x, ctx, residual, accumulate=True):
+    def forward(self, x, ctx, residual, accumulate=True, defer=False):
         F, T = self.hidden, ctx.n_tokens
         act = ctx.buf("ffn_act", (ctx.token_capacity, F), self.dtype)
         if self.bias:
             if accumulate:
                 raise ValueError("a biased feed-forward hands its result to a block that adds the down bias")
             n = self.w_gate_up.shape[0]
-            gu = ctx.buf("ffn_gate_up_f32", (ctx.token_capacity, n), torch.float32)
-            linear(x, self.w_gate_up, gu, STORE_F32, ctx, M=T)
-            self.extra_out = gu[:, 2 * F:] if n > 2 * F else None
-            ops.bias_glu(gu, self.w_gate_bias, self.w_up_bias, act, T, F, self.act)
+            # a few tokens: the product stays in partials and the activation kernel sums them
+            part = linear_deferred(x, self.w_gate_up, ctx, T) if ctx.defer_swiglu else None
+            if part is not None:
+                self.extra_out = ctx.buf("ffn_extra", (ctx.token_capacity, n - 2 * F), torch.float32) if n > 2 * F else None
+                ops.bias_glu_reduce(part, self.w_gate_bias, self.w_up_bias, act, T, F, self.act, extra=self.extra_out)
+            else:
+                gu = ctx.buf("ffn_gate_up_f32", (ctx.token_capacity, n), torch.float32)
+                linear(x, self.w_gate_up, gu, STORE_F32, ctx, M=T)
+                self.extra_out = gu[:, 2 * F:] if n > 2 * F else None
+                ops.bias_glu(gu, self.w_gate_bias, self.w_up_bias, act, T, F, self.act)
+            if defer and not accumulate:
+                part = linear_deferred(act, self.w_down_weight, ctx, T)
+                if part is not None:
+                    return part
         elif ops.gemm_tc_supported(x, self.w_gate_up):
             linear_swiglu(x, self.w_gate_up, act, F, ctx, M=T)
         else:
@@ -78,3 +88,4 @@ class SwiGLU(FeedForward):
             linear(x, self.w_gate_up, gu, STORE, ctx, M=T)
             ops.swiglu(gu, act, T, F)
         linear(act, self.w_down_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
+        return None

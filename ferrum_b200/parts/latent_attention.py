@@ -24,7 +24,7 @@ import torch
 from ..ops import lib as ops
 from . import attention_plan
 from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
-from .linear import RESIDUAL, STORE, STORE_F32, linear
+from .linear import RESIDUAL, STORE, STORE_F32, linear, linear_deferred
 
 
 # Steps of single tokens cut every token's keys among CTAs while they bring fewer rows than this per SM.
@@ -75,22 +75,26 @@ class LatentAttention(Mixer):
     def cache_need(self):
         return CacheNeed(paged=PagedKVNeed(1, self.Dk, self.window, parts=1))
 
-    def forward(self, x, ctx, cache, residual, accumulate=True):
+    def forward(self, x, ctx, cache, residual, accumulate=True, defer=False):
         T, H, Dn, Rr, Dv, R, Rq, Dk = ctx.n_tokens, self.H, self.Dn, self.Rr, self.Dv, self.R, self.Rq, self.Dk
         cap = ctx.token_capacity
         writes = self.own_latent
         if writes != cache.writes:
             raise ValueError("a latent mixer without a key/value projection runs as a reader of another run's cache "
                              "(and one with it as a writer)")
-        proj = ctx.buf("lat_proj", (cap, self.w_in.shape[0]), torch.float32)
-        linear(x, self.w_in, proj, STORE_F32, ctx, M=T)
+        # a few tokens: the product stays in partials and the next kernel sums them while it reads
+        part = linear_deferred(x, self.w_in, ctx, T) if ctx.defer_residuals else None
+        proj = None
+        if part is None:
+            proj = ctx.buf("lat_proj", (cap, self.w_in.shape[0]), torch.float32)
+            linear(x, self.w_in, proj, STORE_F32, ctx, M=T)
         cq = ctx.buf("lat_cq", (cap, Rq), self.dtype)
         gate = ctx.buf("lat_gate", (cap, H), torch.float32)
         table = ctx.block_tables[cache.group]
         off_gate = Rq + (Dk if writes else 0)
         ops.latent_prep(proj, T, 0, Rq, self.w_dq_norm_weight, Rq if writes else -1, R, Rr,
                         self.w_dkv_norm_weight if writes else None, off_gate, H, ctx, table, self.rotary, cache.plane,
-                        cache.page_stride, cache.page_size, cq, gate, self.eps)
+                        cache.page_stride, cache.page_size, cq, gate, self.eps, partials=part)
         q = ctx.buf("lat_q", (cap, H * (Dn + Rr)), self.dtype)
         linear(cq, self.w_uq_weight, q, STORE, ctx, M=T)
         qf = ctx.buf("lat_qf", (cap, H * Dk), self.dtype)
@@ -124,4 +128,9 @@ class LatentAttention(Mixer):
         else:
             for h in range(H):
                 linear(o[:, h * R:(h + 1) * R], self.w_uv_h[h], ov[:, h * Dv:(h + 1) * Dv], STORE, ctx, M=T)
+        if defer and not accumulate:
+            part = linear_deferred(ov, self.w_o_weight, ctx, T)
+            if part is not None:
+                return part
         linear(ov, self.w_o_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
+        return None

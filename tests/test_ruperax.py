@@ -142,3 +142,17 @@ def test_plain_window_is_exact_by_hand():
     out = P.latent_attention(m, w, "p.", mix, 1e-6, np.arange(5), (c, np.zeros((5, 0))))
     want = np.array([c[0], c[:2].mean(0), c[:3].mean(0), c[1:4].mean(0), c[2:5].mean(0)]) * 0.5     # scale 0: plain means; gate 1/2
     assert np.allclose(out, want)
+
+
+def test_command_line_writes_and_lists_a_random_model(tmp_path, capsys):
+    from ferrum_b200 import cli
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(RUPERAX_B))
+    out = tmp_path / "model"
+    assert cli.main(["random-weights", "--config", str(cfg), "--out", str(out), "--seed", "3", "--dtype", "bfloat16"]) == 0
+    capsys.readouterr()
+    assert cli.main(["dump", str(out)]) == 0
+    listing = capsys.readouterr().out
+    assert "l2.mix.uk [128, 128] bfloat16" in listing and "l3.rg1.b [128] float32" in listing and "l3.norm2" not in listing
+    c, w = P.read_model(str(out))
+    assert c["architecture"] == "Ruperax" and w["head"].shape == (256, 128)

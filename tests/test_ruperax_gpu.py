@@ -431,3 +431,31 @@ def test_greedy_generation_through_the_engine(cuda, folders, name, dtype):
                 assert logits.max() - logits[t] <= 0.2 * logits.std(), (len(seq), t)
             seq.append(t)
     assert eng.stats()["pages_used"] == [0] * eng.cache.manager.n_groups
+
+
+def test_trace_run_program_and_command_line(cuda, folders, tmp_path):
+    """bin/trace_run as a user runs it on a Ruperax folder (a subprocess, JSON lines in, .f32 files
+    out), and `ferrum generate` on the same folder against the plain implementation."""
+    import json, os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    toks = tokens_for("A", 40, 16)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": toks[30:], "want": []}, {"id": "y", "tokens": toks[:2], "want": [1]}], "end": ["y"]},
+             {"step": 2, "entries": [{"id": "x", "tokens": toks[:1], "want": [0]}], "end": ["x"]}]
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders["A"], "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.split() == ["done", "0", "done", "1", "done", "2"]
+    ref = plain(folders["A"], "float32", toks + toks[:1])
+    assert_close_f32(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1), ref[[0, 29]], "trace_run step 0")
+    assert_close_f32(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1), ref[[1]], "trace_run step 1")
+    assert_close_f32(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1), ref[[40]], "trace_run step 2")
+    cfg, w = P.read_model(folders["A"])
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "ferrum"), "generate", "--model", folders["A"], "--dtype", "float32",
+                        "--prompt-tokens", ",".join(str(t) for t in toks[:12]), "--max-new-tokens", "6"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    want = P.generate(cfg, w, toks[:12], 6)
+    assert ",".join(str(t) for t in want) in p.stdout.replace(" ", ""), (p.stdout, want)

@@ -459,3 +459,17 @@ def test_trace_run_program_and_command_line(cuda, folders, tmp_path):
     assert p.returncode == 0, p.stderr[-2000:]
     want = P.generate(cfg, w, toks[:12], 6)
     assert ",".join(str(t) for t in want) in p.stdout.replace(" ", ""), (p.stdout, want)
+
+
+@pytest.mark.parametrize("name", list(RUPERAX))
+def test_float16_prefill_and_decoding(cuda, folders, name):
+    """The 16-bit kernels with float16 storage (weights, activations, cached rows): a prompt, then
+    single tokens, against exact arithmetic on the stored weights."""
+    toks = tokens_for(name, 150, 14)
+    cfg, w = P.read_model(folders[name])
+    ref = P.forward(cfg, w, toks)
+    r = Replay(session(folders[name], "float16", 192))
+    r.step([("a", toks[:100], "all")])
+    for t in toks[100:]:
+        r.step([("a", [t], "all")])
+    assert_close_16bit(r.logits("a", len(toks)), ref, f"{name} float16", "float16")

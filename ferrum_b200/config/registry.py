@@ -87,3 +87,5 @@ def _ensure_builtin():
         from ..models import llama  # noqa: F401  (registers itself)
     if "Ruperax" not in _REGISTRY:
         from ..models import ruperax  # noqa: F401
+    if "Vikupel" not in _REGISTRY:
+        from ..models import vikupel  # noqa: F401

@@ -81,6 +81,20 @@ __device__ __forceinline__ float4 ag_load4(const T* row, int d, int D, bool vec)
   return r;
 }
 
+// The output goes out in the cache's type, or as float32 when a kernel after this one still works on
+// it (`out_f32`: `out` then points to float rows and ldo counts floats).
+template <typename T>
+__device__ __forceinline__ void ag_store(T* out, size_t idx, float v, int out_f32) {
+  if (out_f32) reinterpret_cast<float*>(out)[idx] = v;
+  else out[idx] = from_f32<T>(v);
+}
+
+// A penalty on distance, taken off the scaled score: bias1[h] * ln(1 + bias2[h] * (pos - key)); no
+// penalty when bias1 is null.
+__device__ __forceinline__ float ag_distance_penalty(const float* bias1, const float* bias2, int h, int dist) {
+  return bias1 == nullptr ? 0.f : bias1[h] * log1pf(bias2[h] * (float)dist);
+}
+
 // part: null (the CTA covers the row's whole key range and writes `out`), or the partials
 // [token][head][split slot][D + 2] of the split that blockIdx.y names.
 // The tile after the one being worked on is on its way meanwhile: float32 rows that are 16-byte
@@ -92,7 +106,8 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
                          const int* __restrict__ positions, const int* __restrict__ req_of_token,
                          const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                          long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
-                         int* __restrict__ err, float* __restrict__ part, int split_slots, int vec) {
+                         int* __restrict__ err, float* __restrict__ part, int split_slots, int vec,
+                         const float* __restrict__ bias1, const float* __restrict__ bias2, int out_f32) {
   using Tile = AgTile<DI>;
   constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
   extern __shared__ __align__(16) float ag_smem[];
@@ -206,7 +221,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
           dot = fmaf(a.z, k4.z, dot);
           dot = fmaf(a.w, k4.w, dot);
         }
-        s = dot * scale;
+        s = dot * scale - ag_distance_penalty(bias1, bias2, h0 + warp, pos - (k_begin + n * TK + lane));
       }
       const float m_new = fmaxf(m, warp_max(s));
       float corr = 1.f, pj = 0.f;
@@ -247,7 +262,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
 #pragma unroll
     for (int i = 0; i < DI; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) out[(size_t)t * ldo + (size_t)h * D + d] = from_f32<T>(l > 0.f ? acc[i] / l : 0.f);
+      if (d < D) ag_store<T>(out, (size_t)t * ldo + (size_t)h * D + d, l > 0.f ? acc[i] / l : 0.f, out_f32);
     }
   } else {
     float* p = part + (((size_t)t * Hq + h) * split_slots + blockIdx.y) * (D + 2);
@@ -296,7 +311,8 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
                                 const int* __restrict__ positions, const int* __restrict__ q_start, int n_reqs,
                                 const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                                 long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
-                                int* __restrict__ err, int vec) {
+                                int* __restrict__ err, int vec, const float* __restrict__ bias1,
+                                const float* __restrict__ bias2, int out_f32) {
   using Tile = AgTile<DI>;
   using TT = AgTokenTile<DI>;
   constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
@@ -453,7 +469,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 #pragma unroll
       for (int i = 0; i < AG_TH; ++i) {
         const bool seen = have && key <= pos[i] && key >= lo[i];
-        const float sv = seen ? sc[i] * scale : -INFINITY;
+        const float sv = seen ? sc[i] * scale - ag_distance_penalty(bias1, bias2, h0 + warp, pos[i] - key) : -INFINITY;
         const float m_new = fmaxf(m[i], warp_max(sv));
         float cr = 1.f, pj = 0.f;
         if (m_new != -INFINITY) {
@@ -503,7 +519,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 #pragma unroll
     for (int e = 0; e < DI; ++e) {
       const int d = lane + 32 * e;
-      if (d < D) out[(size_t)(t0 + i0 + i) * ldo + (size_t)h * D + d] = from_f32<T>(l[i] > 0.f ? acc[i][e] / l[i] : 0.f);
+      if (d < D) ag_store<T>(out, (size_t)(t0 + i0 + i) * ldo + (size_t)h * D + d, l[i] > 0.f ? acc[i][e] / l[i] : 0.f, out_f32);
     }
   }
 }
@@ -512,7 +528,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(32)
 attention_generic_combine_kernel(T* __restrict__ out, int ldo, const float* __restrict__ part, const int* __restrict__ positions,
-                                 int Hq, int D, int window, int split_slots) {
+                                 int Hq, int D, int window, int split_slots, int out_f32) {
   const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
   const int pos = positions[t];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -551,7 +567,7 @@ attention_generic_combine_kernel(T* __restrict__ out, int ldo, const float* __re
 #pragma unroll
   for (int i = 0; i < AG_DI; ++i) {
     const int d = lane + 32 * i;
-    if (d < D) out[(size_t)t * ldo + (size_t)h * D + d] = from_f32<T>(L > 0.f ? O[i] / L : 0.f);
+    if (d < D) ag_store<T>(out, (size_t)t * ldo + (size_t)h * D + d, L > 0.f ? O[i] / L : 0.f, out_f32);
   }
 }
 
@@ -563,13 +579,16 @@ FERRUM_API int ferrum_attention_generic_split() { return AG_SPLIT; }
 // Otherwise `part` holds n_tokens * Hq * split_slots * (D + 2) floats, every row's key range is
 // cut at multiples of 128 keys among split_slots CTAs (split_slots must cover the longest row),
 // and a second launch folds the partials into `out`.
+// bias1, bias2 (float32 per query head on the device, or null): the distance penalty above.  out_f32: the
+// output rows are float32 whatever the cache's type.
 // q_start (n_reqs + 1 entries on the device; may be null): with it and without `part`, tokens of a
 // request that follow each other in the batch share their key tiles (the kernel for prompt portions).
 FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int ldo, int dtype, int n_tokens,
                                         const int* positions, const int* req_of_token, const int* block_table,
                                         int table_width, const void* kv_plane, long long page_stride, int page_size,
                                         int Hq, int Hkv, int D, float scale, int window, int* err_flag, float* part,
-                                        int split_slots, const int* q_start, int n_reqs, cudaStream_t stream) {
+                                        int split_slots, const int* q_start, int n_reqs, const float* bias1,
+                                        const float* bias2, int out_f32, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   FERRUM_CHECK_ARG(D > 0 && D <= AG_MAX_D, "attention: head size %d is outside (0, %d]", D, AG_MAX_D);
   FERRUM_CHECK_ARG(page_size > 0 && table_width > 0 && window >= 0, "attention: bad cache arguments");
@@ -598,7 +617,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     }                                                                                                                   \
     attention_generic_tokens_kernel<T, DI_><<<(unsigned)ctas, AG_TWARPS * 32, AgTokenTile<DI_>::SMEM_BYTES, stream>>>(   \
       (const T*)q, ldq, (T*)out, ldo, positions, q_start, n_reqs, block_table, table_width, (const T*)kv_plane,         \
-      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec);                                                \
+      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec, bias1, bias2, out_f32);                                             \
   })
     if (D <= 32) AG_LAUNCH_TOKENS(1);
     else if (D <= 64) AG_LAUNCH_TOKENS(2);
@@ -621,7 +640,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     }                                                                                                                   \
     attention_generic_kernel<T, DI_><<<grid, AG_WARPS * 32, AgTile<DI_>::SMEM_BYTES, stream>>>(                        \
       (const T*)q, ldq, (T*)out, ldo, positions, req_of_token, block_table, table_width, (const T*)kv_plane, page_stride, \
-      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec);                                          \
+      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec, bias1, bias2, out_f32);                                       \
   })
   if (D <= 32) AG_LAUNCH(1);
   else if (D <= 64) AG_LAUNCH(2);
@@ -633,7 +652,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     const dim3 cgrid(n_tokens, Hq);
     FERRUM_CHECK_ARG(cgrid.y <= 65535, "attention: too many heads");
     FERRUM_DISPATCH_DTYPE(dtype, T, (attention_generic_combine_kernel<T><<<cgrid, 32, 0, stream>>>(
-        (T*)out, ldo, part, positions, Hq, D, window, split_slots)));
+        (T*)out, ldo, part, positions, Hq, D, window, split_slots, out_f32)));
     FERRUM_CHECK_LAUNCH("attention_generic_combine");
   }
   return 0;

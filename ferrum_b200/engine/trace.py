@@ -18,7 +18,7 @@ from .runner import ModelRunner
 
 
 class TraceSession:
-    def __init__(self, model_dir, dtype, max_tokens, page_size=16, max_requests=8):
+    def __init__(self, model_dir, dtype, max_tokens, page_size=16, max_requests=4):
         max_tokens = max(int(max_tokens), page_size)
         # every live request's length is rounded up to whole pages
         self.model, self.dtype = load_model(model_dir, dtype, max_positions=max_tokens)

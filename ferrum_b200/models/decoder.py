@@ -31,12 +31,16 @@ class DecoderModel(Part):
     graph_safe = True
 
     def __init__(self, config, dtype, embedding, position, blocks, final_norm, head, schedule=None,
-                 block_prefix="blk.{}.", names=("token_embd.", "output_norm.", "output.")):
+                 block_prefix="blk.{}.", names=("token_embd.", "output_norm.", "output."), shared=()):
+        """shared: (prefix, part) pairs the model owns because several blocks refer to them (a table
+        that every layer reads a slice of); they only bring parameters, the blocks call them."""
         self.config, self.dtype = config, dtype
         self.embedding, self.position, self.blocks = embedding, position, list(blocks)
         self.final_norm, self.head = final_norm, head
         self.schedule: List[Run] = list(schedule) if schedule is not None else [Run(i) for i in range(len(self.blocks))]
         self._block_prefix, self._names = block_prefix, names
+        self.shared = list(shared)
+        self.on_run = None       # debugging hook: called as on_run(k, h) after run k of the schedule with the residual rows
         for k, run in enumerate(self.schedule):
             if not 0 <= run.block < len(self.blocks):
                 raise ValueError(f"schedule entry {k} names block {run.block}, which does not exist")
@@ -48,6 +52,7 @@ class DecoderModel(Part):
         out = [(self._names[0], self.embedding)]
         if self.position is not None:
             out.append(("position.", self.position))
+        out += self.shared
         out += [(self._block_prefix.format(i), b) for i, b in enumerate(self.blocks)]
         out += [(self._names[1], self.final_norm), (self._names[2], self.head)]
         return out
@@ -85,6 +90,9 @@ class DecoderModel(Part):
             if NVTX:
                 torch.cuda.nvtx.range_push(f"run {k} block {run.block}")
             self.blocks[run.block].forward(h, ctx, cache.layer_cache(k))
+            if self.on_run is not None:
+                ctx.flush_residual()
+                self.on_run(k, h)
             if NVTX:
                 torch.cuda.nvtx.range_pop()
         if ctx.n_want == 0:

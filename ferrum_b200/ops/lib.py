@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 9
+ABI = 10
 
 
 def lib():
@@ -397,15 +397,26 @@ def attention_generic_split():
 
 
 def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv_plane, page_stride, page_size, Hq,
-                      Hkv, D, scale, window, err, part=None, split_slots=0, q_start=None, n_reqs=0):
+                      Hkv, D, scale, window, err, part=None, split_slots=0, q_start=None, n_reqs=0, distance_penalty=None):
     """Causal GQA attention of every token over its request's pages on the CUDA cores, float32
     arithmetic.  part=None: one CTA per (token, group of heads) walks the whole key range (many
     tokens).  With `part` (float32, n_tokens * Hq * split_slots * (D + 2) elements) every row's keys
     are cut at multiples of `attention_generic_split()` among split_slots CTAs and folded by a
     second launch (few tokens); split_slots must cover the longest row.  With q_start (the device's
     n_reqs + 1 token offsets of the requests, tokens of a request in ascending positions) and no
-    `part`, up to eight tokens of a request that follow each other share every tile of keys."""
-    _need(q, None, "q", 2); _need(out, q.dtype, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
+    `part`, up to eight tokens of a request that follow each other share every tile of keys.
+    distance_penalty=(r1, r2), float32 per query head: r1[h] * ln(1 + r2[h] * (position - key position))
+    is taken off the scaled score.  `out` may be float32 whatever the cache's type (a kernel after
+    this one still works on the heads' results)."""
+    _need(q, None, "q", 2); _need(out, None, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
+    if out.dtype not in (q.dtype, torch.float32):
+        raise KernelError(f"attention: out must be {q.dtype} or float32, found {out.dtype}")
+    r1 = r2 = None
+    if distance_penalty is not None:
+        r1, r2 = distance_penalty
+        _need(r1, torch.float32, "r1", 1); _need(r2, torch.float32, "r2", 1)
+        if r1.shape[0] != Hq or r2.shape[0] != Hq:
+            raise KernelError("attention: the distance penalty has one pair of numbers per query head")
     _need(positions, torch.int32, "positions", 1); _need(req_of_token, torch.int32, "req_of_token", 1)
     _need(block_table, torch.int32, "block_table", 2)
     if not block_table.is_contiguous():
@@ -419,7 +430,9 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_plane),
                                           c_longlong(page_stride), c_int(page_size), c_int(Hq), c_int(Hkv), c_int(D),
                                           c_float(scale), c_int(window), _ptr(err), _ptr(part), c_int(split_slots),
-                                          _ptr(q_start) if part is None else None, c_int(n_reqs), _stream()),
+                                          _ptr(q_start) if part is None else None, c_int(n_reqs), _ptr(r1), _ptr(r2),
+                                          c_int(1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0),
+                                          _stream()),
            "attention_generic")
 
 
@@ -739,3 +752,96 @@ def head_linear(x, x_head_stride, w, y, y_head_stride, n_tokens):
     _check(lib().ferrum_head_linear(_ptr(x), c_int(x.stride(0)), c_int(x_head_stride), _ptr(w), _ptr(y), c_int(y.stride(0)),
                                     c_int(y_head_stride), dtype_code(x.dtype), c_int(n_tokens), c_int(H), c_int(N), c_int(K),
                                     _stream()), "head_linear")
+
+
+# ----------------------------------------------------------------------------- shaped attention heads
+def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, value_pairing, unit_norm, eps, q_out, plane,
+              page_stride, page_size, Hq, Hkv, Dk, Dv, Dp, writes):
+    """Per head of a float32 product row [q | k | v | ...]: rotary turn of q and k (table `rot`:
+    `.cos_sin` [positions, R/2, 2], `.rope_dim`; None: none), optional division by the head's root
+    mean square, a turn of the value over all its elements (`value_rot`: a table [positions, Dv/2, 2]
+    or None); q -> q_out [T, Hq * Dp], k and v -> the token's place in the cache (rows of Dp elements)."""
+    _need(proj, torch.float32, "proj", 2); _need(q_out, plane.dtype, "q_out", 2); _need(block_table, torch.int32, "block_table", 2)
+    if proj.shape[1] < Hq * Dk + (Hkv * (Dk + Dv) if writes else 0) or q_out.shape[1] < Hq * Dp:
+        raise KernelError("qkv_shape: a row is too short for the heads")
+    cs = rot.cos_sin if rot is not None else None
+    _check(lib().ferrum_qkv_shape(_ptr(proj), c_int(proj.stride(0)), c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.req_of_token),
+                                  _ptr(block_table), c_int(block_table.shape[1]), _ptr(cs), c_int(rot.rope_dim if rot is not None else 0),
+                                  c_int(qk_pairing), c_int(cs.shape[0] if cs is not None else 0), _ptr(value_rot),
+                                  c_int(value_pairing), c_int(value_rot.shape[0] if value_rot is not None else 0),
+                                  c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), c_int(q_out.stride(0)), _ptr(plane),
+                                  c_longlong(page_stride), c_int(page_size), dtype_code(plane.dtype), c_int(Hq), c_int(Hkv),
+                                  c_int(Dk), c_int(Dv), c_int(Dp), c_int(1 if writes else 0), _ptr(ctx.err), _stream()),
+           "qkv_shape")
+
+
+def attention_finish(o, n_tokens, ctx, value_rot, value_pairing, gate, out, Hq, Dv, Dp):
+    """out[t, h] = turn_back(o[t, h], position) * sigmoid(gate[t, h]) in the compute type; `value_rot`
+    (None: no turn) and `gate` (float32 logits [T, Hq * Dv], may be a view into wider rows; None: no gate)."""
+    _need(o, torch.float32, "o", 2); _need(out, None, "out", 2)
+    if gate is not None:
+        _need(gate, torch.float32, "gate", 2)
+    _bytes_work((o, n_tokens), (out, n_tokens))
+    _check(lib().ferrum_attention_finish(_ptr(o), c_int(o.stride(0)), c_int(n_tokens), _ptr(ctx.positions), _ptr(value_rot),
+                                         c_int(value_pairing), c_int(value_rot.shape[0] if value_rot is not None else 0),
+                                         _ptr(gate), c_int(gate.stride(0) if gate is not None else 0), _ptr(out),
+                                         c_int(out.stride(0)), dtype_code(out.dtype), c_int(Hq), c_int(Dv), c_int(Dp),
+                                         _ptr(ctx.err), _stream()), "attention_finish")
+
+
+# ----------------------------------------------------------------------------- state-space mixer
+def mamba2_mix(proj, n_tokens, ctx, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w, heads, P, N, groups, norm_groups, eps,
+               state, xbc, y, out):
+    """Everything of the state-space mixer between its two products: short convolution + silu over
+    x, B, C (its last inputs kept in the request's state row), the recurrence per head, the gate by
+    silu(z) and the grouped RMS norm.  proj: float32 rows [z | x | B | C | dt]; state: float32
+    [max_requests, heads * P * N + (taps - 1) * channels]; xbc, y: float32 scratch; out: compute type."""
+    global launches
+    _need(proj, torch.float32, "proj", 2); _need(state, torch.float32, "state", 2); _need(out, None, "out", 2)
+    inner, C = heads * P, heads * P + 2 * groups * N
+    taps = conv_w.shape[1]
+    for t, n in ((conv_w, "conv_w"), (conv_b, "conv_b"), (dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip"), (norm_w, "norm_w")):
+        _need(t, torch.float32, n)
+    if (proj.shape[1] < inner + C + heads or conv_w.shape[0] != C or state.shape[1] != inner * N + (taps - 1) * C
+            or xbc.numel() < n_tokens * C or y.numel() < n_tokens * inner or out.shape[1] != inner or not conv_w.is_contiguous()):
+        raise KernelError("mamba2_mix: shapes do not agree")
+    _check(lib().ferrum_mamba2_mix(_ptr(proj), c_int(proj.stride(0)), c_int(n_tokens), c_int(ctx.n_reqs), _ptr(ctx.req_of_token),
+                                   _ptr(ctx.q_start), _ptr(ctx.slots), _ptr(conv_w), _ptr(conv_b), c_int(taps), _ptr(dt_bias),
+                                   _ptr(a_log), _ptr(d_skip), _ptr(norm_w), c_int(heads), c_int(P), c_int(N), c_int(groups),
+                                   c_int(norm_groups), c_float(eps), _ptr(state), c_longlong(state.stride(0)), _ptr(xbc), _ptr(y),
+                                   _ptr(out), c_int(out.stride(0)), dtype_code(out.dtype), _stream()), "mamba2_mix")
+    launches += 3 if taps > 1 else 2       # (the entry point launches the convolution, its state, the walk and the norm)
+
+
+# ----------------------------------------------------------------------------- parallel block
+def scaled_sum(x, y1, y2, mult, n_tokens, xc=None):
+    """x[:n] += mult * (y1 + y2) in float32 (y2 may be None); xc, when given, also receives the new rows
+    in its own type."""
+    _need(x, torch.float32, "x", 2); _need(y1, torch.float32, "y1", 2)
+    E = x.shape[1]
+    ok = x.is_contiguous() and y1.is_contiguous() and y1.shape[1] == E and (y2 is None or (y2.is_contiguous() and y2.shape[1] == E))
+    if not ok or (xc is not None and (not xc.is_contiguous() or xc.shape[1] != E)):
+        raise KernelError("scaled_sum: rows must be contiguous and of one width")
+    _bytes_work((x, 2 * n_tokens), (y1, n_tokens), (y2, n_tokens), (xc, n_tokens))
+    _check(lib().ferrum_scaled_sum(_ptr(x), _ptr(y1), _ptr(y2), c_float(mult), _ptr(xc),
+                                   dtype_code(xc.dtype if xc is not None else torch.float32), c_int(n_tokens), c_int(E), _stream()),
+           "scaled_sum")
+
+
+def gated_table_rows(s, table, token_ids, offset, dim, out, n_tokens, err):
+    """out[t, j] = gelu_tanh(s[t, j]) * table[token_ids[t], offset + j]; s float32, table and out in the compute type."""
+    _need(s, torch.float32, "s", 2); _need(table, out.dtype, "table", 2); _need(token_ids, torch.int32, "token_ids", 1)
+    _check(lib().ferrum_gated_table_rows(_ptr(s), c_int(s.stride(0)), _ptr(table), c_int(table.stride(0)), c_int(table.shape[0]),
+                                         _ptr(token_ids), c_int(offset), c_int(dim), _ptr(out), c_int(out.stride(0)),
+                                         dtype_code(out.dtype), c_int(n_tokens), _ptr(err), _stream()), "gated_table_rows")
+
+
+def norm_scaled_add(x, y, w, mult, eps, n_tokens):
+    """x[:n] += mult * y / sqrt(mean(y^2) + eps) * w, all float32."""
+    _need(x, torch.float32, "x", 2); _need(y, torch.float32, "y", 2); _need(w, torch.float32, "w", 1)
+    E = x.shape[1]
+    if y.shape[1] != E or w.shape[0] != E or not x.is_contiguous() or not y.is_contiguous():
+        raise KernelError("norm_scaled_add: shapes do not agree")
+    _bytes_work((x, 2 * n_tokens), (y, n_tokens))
+    _check(lib().ferrum_norm_scaled_add(_ptr(x), _ptr(y), _ptr(w), c_float(mult), c_float(eps), c_int(n_tokens), c_int(E), _stream()),
+           "norm_scaled_add")

@@ -83,7 +83,7 @@ class PagedAttention(Mixer):
             self._generic(qkv, out, ctx, cache, table)
         linear(out, self.w_output_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
 
-    def _generic(self, qkv, out, ctx, cache, table):
+    def _generic(self, qkv, out, ctx, cache, table, distance_penalty=None):
         """CUDA-core path.  With enough rows to fill the GPU (a prompt portion) every row walks its
         keys alone; with few (decoding) the keys of a row are cut into splits among CTAs.  Which of
         the two runs depends on the number of tokens only, and so does the number of split slots
@@ -101,7 +101,7 @@ class PagedAttention(Mixer):
             part = ctx.buf("attn_generic_part", (T * Hq * slots * (D + 2),), torch.float32)
         ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
                               cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err, part, slots,
-                              q_start=ctx.q_start, n_reqs=ctx.n_reqs)
+                              q_start=ctx.q_start, n_reqs=ctx.n_reqs, distance_penalty=distance_penalty)
 
     def plan(self, ctx, cache):
         """The step's work lists of the tensor-core kernels for this layer's shape (None on the

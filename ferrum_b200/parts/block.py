@@ -152,3 +152,90 @@ class ParallelGatedBlock(Part):
         ops.gated_residual(h, T, y1 if p1 is None else None, g1, self.w_rg1_bias, y2 if p2 is None else None, c2, g2,
                            self.w_rg2_bias if y2 is not None else None,
                            ctx=ctx, stage=stage, state=state, p1=p1, p2=p2)
+
+
+class TokenSideTable(Part):
+    """A second embedding table [vocabulary, layers * dim]: layer i's `TokenSideInput` reads columns
+    i * dim .. (i + 1) * dim of a token's row.  One table serves all layers, so the model owns it."""
+    graph_safe = True
+
+    def __init__(self, n_vocab, total_dim):
+        self.n_vocab, self.total_dim = int(n_vocab), int(total_dim)
+        self.w_weight = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.n_vocab, self.total_dim))}
+
+
+class TokenSideInput(Part):
+    """A token-dependent input added to the residual stream x after a block's sublayers:
+
+        g = gelu_tanh(W_gate x) * table[token][offset : offset + dim];   y = W_proj g
+        x += mult * y / sqrt(mean(y^2) + eps) * w
+
+    The norm is a plain-weight RMS norm of the branch's result.  `table` is the model's `TokenSideTable`."""
+    graph_safe = True
+
+    def __init__(self, width, dim, offset, table: TokenSideTable, eps, dtype):
+        if offset < 0 or offset + dim > table.total_dim:
+            raise ValueError(f"columns {offset}..{offset + dim} are outside the side table's {table.total_dim}")
+        self.width, self.dim, self.offset, self.table, self.eps, self.dtype = width, int(dim), int(offset), table, float(eps), dtype
+        self.w_gate_weight = self.w_proj_weight = self.w_norm_weight = None
+
+    def param_specs(self):
+        return {"gate.weight": ParamSpec((self.dim, self.width)), "proj.weight": ParamSpec((self.width, self.dim)),
+                "norm.weight": ParamSpec((self.width,), kind="vector", init="ones_normal")}
+
+    def forward(self, h, x_in, ctx, mult):
+        """h: the float32 residual rows (updated in place); x_in: the same rows in the compute type."""
+        T, cap = ctx.n_tokens, ctx.token_capacity
+        s = ctx.buf("side_s", (cap, self.dim), torch.float32)
+        linear(x_in, self.w_gate_weight, s, STORE_F32, ctx, M=T)
+        g = ctx.buf("side_g", (cap, self.dim), self.dtype)
+        ops.gated_table_rows(s, self.table.w_weight, ctx.token_ids, self.offset, self.dim, g, T, ctx.err)
+        y = ctx.buf("side_y", (cap, self.width), torch.float32)
+        linear(g, self.w_proj_weight, y, STORE_F32, ctx, M=T)
+        ops.norm_scaled_add(h, y, self.w_norm_weight, mult, self.eps, T)
+
+
+class ParallelBlock(Part):
+    """Both sublayers read ONE norm of the residual row and their sum is scaled on its way in:
+
+        n = norm1(x);   x += mult * (mixer(n) + ffn(n))
+
+    then, when the block has one, a `TokenSideInput` adds its token-dependent branch (scaled by the
+    same `mult`).  `ffn` may be None.  The sublayers hand their results over in float32 buffers and
+    one kernel makes the scaled sum (and, for the side input's product, the new row in the compute
+    type).  The reference's block is sequential (`PreNormBlock`)."""
+    graph_safe = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, ffn: FeedForward = None, mult=1.0, side: TokenSideInput = None,
+                 names=("norm1.", "mix.", "mlp.", "side.")):
+        self.norm1, self.mixer, self.ffn, self.mult, self.side = norm1, mixer, ffn, float(mult), side
+        self._names = names
+
+    def children(self):
+        out = [(self._names[0], self.norm1), (self._names[1], self.mixer)]
+        if self.ffn is not None:
+            out.append((self._names[2], self.ffn))
+        if self.side is not None:
+            out.append((self._names[3], self.side))
+        return out
+
+    def forward(self, h, ctx, cache):
+        T, cap, E = ctx.n_tokens, ctx.token_capacity, h.shape[1]
+        x = self.norm1.forward(h, ctx)
+        ctx.flush_residual()
+        y1 = ctx.buf("par_y1", (cap, E), torch.float32)
+        self.mixer.forward(x, ctx, cache, y1, accumulate=False)
+        y2 = None
+        if self.ffn is not None:
+            y2 = ctx.buf("par_y2", (cap, E), torch.float32)
+            self.ffn.forward(x, ctx, y2, accumulate=False)
+        ctx.flush_residual()
+        xc = None
+        if self.side is not None and self.side.dtype != torch.float32:
+            xc = ctx.buf("par_xc", (cap, E), self.side.dtype)
+        ops.scaled_sum(h, y1, y2, self.mult, T, xc)
+        if self.side is not None:
+            self.side.forward(h, xc if xc is not None else h, ctx, self.mult)

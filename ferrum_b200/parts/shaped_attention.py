@@ -1,0 +1,89 @@
+"""Grouped-query attention over the paged cache whose heads are shaped before and after the softmax.
+
+What a configuration may switch on, each with its constants as parameters:
+
+  rotary         q and k turn over their leading `rope_dim` elements (a `RotaryEmbedding`, which also
+                 carries the pairing and any scaling of the frequencies); None: positions enter otherwise
+  unit_norm      after the turn, every q and k head is divided by its root mean square (no weight)
+  value_rotary   the value of position j turns by j over all of its elements before it is cached, and
+                 every head's result at position i turns back by i (a `RotaryEmbedding` over vdim)
+  distance_penalty   r1[h] * ln(1 + r2[h] * (i - j)) is taken off the scaled score (r1, r2: tensors)
+  gate           the heads' results are multiplied by sigmoid(W_g x) before the output projection
+  window         a query sees itself and the window - 1 keys before it (0: all)
+  dim != vdim    key and value heads of different sizes share pages of max(dim, vdim)-element rows
+
+Scores, softmax weights, the weighted sum, rotations, the unit norm and the gate are float32 whatever
+the compute type (the CUDA-core attention kernel; keys, values and queries are stored in the compute
+type).  One product makes [q | k | v | gate logits] as float32 rows, `qkv_shape` shapes the heads
+and writes the cache, the attention kernel leaves float32 results, `attention_finish` turns them back,
+gates them and rounds once for the output projection.  The reference's attention has none of these
+(crates/model/src/llama.rs:185-257).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import lib as ops
+from .attention import PagedAttention
+from .base import CacheNeed, PagedKVNeed, ParamSpec
+from .linear import RESIDUAL, STORE_F32, linear
+
+
+class ShapedAttention(PagedAttention):
+    graph_safe = True       # the CUDA-core attention kernel reads no work lists
+
+    def __init__(self, width, n_head, n_head_kv, dim, vdim, dtype, scale, eps=1e-6, window=0, rotary=None, unit_norm=False,
+                 value_rotary=None, distance_penalty=False, gate=False):
+        super().__init__(width, n_head, n_head_kv, max(int(dim), int(vdim)), rotary, dtype, window=window, scale=scale)
+        self.Dk, self.Dv, self.eps = int(dim), int(vdim), float(eps)
+        self.unit_norm, self.value_rotary = bool(unit_norm), value_rotary
+        self.has_penalty, self.has_gate = bool(distance_penalty), bool(gate)
+        if rotary is not None and rotary.rope_dim > self.Dk:
+            raise ValueError("the rotary table turns more elements than a key head has")
+        if value_rotary is not None and value_rotary.rope_dim != self.Dv:
+            raise ValueError("the value rotation covers all of a value head")
+        self.w_r1 = self.w_r2 = self.w_g_weight = None
+        self.w_in = None
+
+    def param_specs(self):
+        E = self.width
+        out = {"q.weight": ParamSpec((self.Hq * self.Dk, E)), "k.weight": ParamSpec((self.Hkv * self.Dk, E)),
+               "v.weight": ParamSpec((self.Hkv * self.Dv, E)), "output.weight": ParamSpec((E, self.Hq * self.Dv))}
+        if self.has_penalty:
+            out["r1"] = ParamSpec((self.Hq,), kind="vector", init="uniform")
+            out["r2"] = ParamSpec((self.Hq,), kind="vector", init="uniform")
+        if self.has_gate:
+            out["g.weight"] = ParamSpec((self.Hq * self.Dv, E))
+        return out
+
+    def finalize(self):
+        rows = [self.w_q_weight, self.w_k_weight, self.w_v_weight] + ([self.w_g_weight] if self.has_gate else [])
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_q_weight = self.w_k_weight = self.w_v_weight = self.w_g_weight = None
+
+    def cache_need(self):
+        return CacheNeed(paged=PagedKVNeed(self.Hkv, self.D, self.window))
+
+    def plan(self, ctx, cache):
+        return None
+
+    def forward(self, x, ctx, cache, residual, accumulate=True, defer=False):
+        T, Hq, Hkv, Dk, Dv, Dp = ctx.n_tokens, self.Hq, self.Hkv, self.Dk, self.Dv, self.D
+        cap = ctx.token_capacity
+        proj = ctx.buf("sattn_proj", (cap, self.w_in.shape[0]), torch.float32)
+        linear(x, self.w_in, proj, STORE_F32, ctx, M=T)
+        table = ctx.block_tables[cache.group]
+        q = ctx.buf("sattn_q", (cap, Hq * Dp), self.dtype)
+        rot, vrot = self.position, self.value_rotary
+        ops.qkv_shape(proj, T, ctx, table, rot, rot.pairing if rot is not None else 0,
+                      vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0, self.unit_norm,
+                      self.eps, q, cache.plane, cache.page_stride, cache.page_size, Hq, Hkv, Dk, Dv, Dp, cache.writes)
+        o = ctx.buf("sattn_o", (cap, Hq * Dp), torch.float32)
+        self._generic(q, o, ctx, cache, table, (self.w_r1, self.w_r2) if self.has_penalty else None)
+        out = ctx.buf("sattn_out", (cap, Hq * Dv), self.dtype)
+        off = Hq * Dk + Hkv * (Dk + Dv)
+        gate = proj[:, off:off + Hq * Dv] if self.has_gate else None
+        ops.attention_finish(o, T, ctx, vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0,
+                             gate, out, Hq, Dv, Dp)
+        linear(out, self.w_output_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
+        return None

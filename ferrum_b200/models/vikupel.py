@@ -48,7 +48,7 @@ def build_vikupel(config: VikupelConfig, dtype, device, max_positions=None):
                                     gate=m.gate)
         else:
             mixer = Mamba2Mixer(E, m.heads, m.vdim, m.state, m.groups, m.norm_groups, m.conv, c.norm_eps, dtype)
-        ffn = SwiGLU(E, layer.mlp.ff, dtype) if layer.mlp is not None else None
+        ffn = SwiGLU(E, layer.mlp.ff, dtype, wide_products=True) if layer.mlp is not None else None
         side = TokenSideInput(E, c.side_dim, i * c.side_dim, side_table, c.norm_eps, dtype) if side_table is not None else None
         blocks.append(ParallelBlock(RMSNorm(E, c.norm_eps, dtype), mixer, ffn, mult=c.residual_mult, side=side))
     schedule = [Run(i) for i in c.run_order()]
@@ -58,21 +58,31 @@ def build_vikupel(config: VikupelConfig, dtype, device, max_positions=None):
     return DecoderModel(c, dtype, emb, None, blocks, RMSNorm(E, c.norm_eps, dtype), head, schedule=schedule, shared=shared)
 
 
-_ATTENTION = {"mix.q": "mix.q.weight", "mix.k": "mix.k.weight", "mix.v": "mix.v.weight", "mix.o": "mix.output.weight",
-              "mix.r1": "mix.r1", "mix.r2": "mix.r2", "mix.g": "mix.g.weight"}
+_ATTENTION = {"mix.q": "mix.q.weight", "mix.k": "mix.k.weight", "mix.v": "mix.v.weight", "mix.o": "mix.output.weight"}
+_PENALTY = {"mix.r1": "mix.r1", "mix.r2": "mix.r2"}
+_GATE = {"mix.g": "mix.g.weight"}
 _MAMBA2 = {"mix.in": "mix.in.weight", "mix.conv": "mix.conv.weight", "mix.conv.b": "mix.conv.bias", "mix.dt_bias": "mix.dt_bias",
            "mix.A_log": "mix.A_log", "mix.D": "mix.D", "mix.norm": "mix.norm.weight", "mix.o": "mix.o.weight"}
-_REST = {"norm1": "norm1.weight", "mlp.gate": "mlp.gate.weight", "mlp.up": "mlp.up.weight", "mlp.down": "mlp.down.weight",
-         "side.gate": "side.gate.weight", "side.proj": "side.proj.weight", "side.norm": "side.norm.weight"}
+_MLP = {"mlp.gate": "mlp.gate.weight", "mlp.up": "mlp.up.weight", "mlp.down": "mlp.down.weight"}
+_SIDE = {"side.gate": "side.gate.weight", "side.proj": "side.proj.weight", "side.norm": "side.norm.weight"}
 
 
 def file_names(config: VikupelConfig):
-    """{name in the checkpoint: canonical name}."""
-    out = {"embed": "token_embd.weight", "side.embed": "side_embd.weight", "final.norm": "output_norm.weight",
-           "head": "output.weight"}
+    """{name in the checkpoint: canonical name}, for the tensors this configuration has."""
+    out = {"embed": "token_embd.weight", "final.norm": "output_norm.weight", "head": "output.weight"}
+    if config.side_dim:
+        out["side.embed"] = "side_embd.weight"
     for i, layer in enumerate(config.layers):
-        names = dict(_REST)
-        names.update(_ATTENTION if isinstance(layer.mixer, AttentionSpec) else _MAMBA2)
+        names = {"norm1": "norm1.weight"}
+        m = layer.mixer
+        if isinstance(m, AttentionSpec):
+            names.update(_ATTENTION)
+            names.update(_PENALTY if m.distance_penalty else {})
+            names.update(_GATE if m.gate else {})
+        else:
+            names.update(_MAMBA2)
+        names.update(_MLP if layer.mlp is not None else {})
+        names.update(_SIDE if config.side_dim else {})
         for short, ours in names.items():
             out[f"l{i}.{short}"] = f"blk.{i}.{ours}"
     return out

@@ -25,12 +25,16 @@ from .linear import RESIDUAL, STORE, STORE_F32, linear, linear_deferred, linear_
 class SwiGLU(FeedForward):
     graph_safe = True
 
-    def __init__(self, width, hidden, dtype, bias=False, act="silu"):
+    def __init__(self, width, hidden, dtype, bias=False, act="silu", wide_products=False):
+        """wide_products: where gate and up do not run on the fused tensor-core kernel (rows that are no
+        16-byte multiples), they stay float32 until the activation has been applied, so that the
+        activation's input is rounded nowhere; without it that path stores them in the compute type."""
         if act not in ops.GLU_ACTS:
             raise ValueError(f"unknown activation {act!r}")
         if act != "silu" and not bias:
             raise ValueError("the fused gate/up kernels apply silu; another activation runs on the biased path")
         self.width, self.hidden, self.dtype, self.bias, self.act = width, hidden, dtype, bool(bias), act
+        self.wide_products = bool(wide_products)
         self.w_gate_weight = self.w_up_weight = self.w_down_weight = None
         self.w_gate_bias = self.w_up_bias = self.w_down_bias = None
         self.w_gate_up = None
@@ -83,6 +87,10 @@ class SwiGLU(FeedForward):
                     return part
         elif ops.gemm_tc_supported(x, self.w_gate_up):
             linear_swiglu(x, self.w_gate_up, act, F, ctx, M=T)
+        elif self.wide_products and self.dtype != torch.float32:
+            gu = ctx.buf("ffn_gate_up_f32", (ctx.token_capacity, 2 * F), torch.float32)
+            linear(x, self.w_gate_up, gu, STORE_F32, ctx, M=T)
+            ops.bias_glu(gu, None, None, act, T, F, self.act)
         else:
             gu = ctx.buf("ffn_gate_up", (ctx.token_capacity, 2 * F), self.dtype)
             linear(x, self.w_gate_up, gu, STORE, ctx, M=T)

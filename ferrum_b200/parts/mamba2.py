@@ -16,11 +16,24 @@ only one).
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..ops import lib as ops
 from .base import CacheNeed, Mixer, ParamSpec, StateNeed
 from .linear import RESIDUAL, STORE_F32, linear
+
+
+def _draw_a_log(shape, g, device, std):
+    """ln of a decay rate drawn from U(1, 16): the usual start of such a layer."""
+    return torch.log(1.0 + 15.0 * torch.rand(shape, generator=g, device=device, dtype=torch.float32))
+
+
+def _draw_dt_bias(shape, g, device, std):
+    """The inverse softplus of a step size drawn log-uniformly from [0.001, 0.1]."""
+    dt = torch.exp(torch.rand(shape, generator=g, device=device, dtype=torch.float32) * math.log(100.0) + math.log(0.001))
+    return dt + torch.log(-torch.expm1(-dt))
 
 
 class Mamba2Mixer(Mixer):
@@ -43,8 +56,8 @@ class Mamba2Mixer(Mixer):
         return {"in.weight": ParamSpec((2 * self.inner + 2 * self.G * self.N + H, E)),
                 "conv.weight": ParamSpec((self.channels, self.taps), kind="vector", init="normal"),
                 "conv.bias": ParamSpec((self.channels,), kind="vector", init="normal"),
-                "dt_bias": ParamSpec((H,), kind="vector", init="normal"),
-                "A_log": ParamSpec((H,), kind="vector", init="normal"),
+                "dt_bias": ParamSpec((H,), kind="vector", init=_draw_dt_bias),
+                "A_log": ParamSpec((H,), kind="vector", init=_draw_a_log),
                 "D": ParamSpec((H,), kind="vector", init="ones_normal"),
                 "norm.weight": ParamSpec((self.inner,), kind="vector", init="ones_normal"),
                 "o.weight": ParamSpec((E, self.inner))}

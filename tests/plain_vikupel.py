@@ -159,13 +159,14 @@ def mixer_window_attention(h, w, p, mc, round_to):
     return matmul((o * gate).reshape(T, H * Dv), w[p + "o"], round_to)
 
 
-def mixer_rotary_attention(h, w, p, mc, eps, round_to, value_layout="halves"):
+def mixer_rotary_attention(h, w, p, mc, eps, round_to):
     """Causal; q and k turn (scaled frequencies) and are then divided by their root mean square per
     head; the value of position j turns by j over all of vdim (unscaled frequencies) and every
     head's output at position i turns back by i."""
     T = h.shape[0]
     H, G, D, Dv = mc["heads"], mc["kv_heads"], mc["dim"], mc["vdim"]
     rot = mc["rot"]
+    value_layout = rot.get("value_layout", "halves")
     pos = torch.arange(T)
     q = matmul(h, w[p + "q"], round_to).view(T, H, D)
     k = matmul(h, w[p + "k"], round_to).view(T, G, D)
@@ -243,7 +244,7 @@ def run_order(cfg):
     return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
 
 
-def layer(x, tokens, i, w, cfg, round_to, value_layout="halves"):
+def layer(x, tokens, i, w, cfg, round_to):
     L = cfg["layers"][i]
     eps, m = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
     h = rms(x, eps) * w[f"l{i}.norm1"][None, :]
@@ -254,7 +255,7 @@ def layer(x, tokens, i, w, cfg, round_to, value_layout="halves"):
     elif kind == "attention":
         y = mixer_window_attention(h, w, p, L["mixer"], round_to)
     elif kind == "attention_2":
-        y = mixer_rotary_attention(h, w, p, L["mixer"], eps, round_to, value_layout)
+        y = mixer_rotary_attention(h, w, p, L["mixer"], eps, round_to)
     else:
         raise ValueError(kind)
     if L.get("mlp") is not None:
@@ -265,12 +266,12 @@ def layer(x, tokens, i, w, cfg, round_to, value_layout="halves"):
     return x
 
 
-def forward(cfg, w, tokens, round_to=None, taps=None, value_layout="halves"):
+def forward(cfg, w, tokens, round_to=None, taps=None):
     """Logits [T, vocab] of one sequence; `taps` (a list) receives the residual stream after every layer run."""
     tokens = torch.as_tensor(tokens, dtype=torch.int64)
     x = rnd(w["embed"], round_to)[tokens].clone()
     for i in run_order(cfg):
-        x = layer(x, tokens, i, w, cfg, round_to, value_layout)
+        x = layer(x, tokens, i, w, cfg, round_to)
         if taps is not None:
             taps.append(x.clone())
     eps = float(cfg["norm"]["eps"])

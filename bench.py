@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--model llama31-8b|llama32-3b|llama2-7b] [--dtype bf16|fp16|fp32]
-                    [--workload decode|serve|latent] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
+                    [--workload decode|serve|latent|hybrid] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
 
 Prints ONE JSON line.
 
@@ -29,6 +29,11 @@ from a CUDA graph costs the host.
 sizes that resemble real models (`--size`), beside a Llama of equal size: prefill of a 2048-token
 prompt, decode at batch 8 with 2048 cached tokens, and per kernel its time, bytes, flops and fraction
 of the measured roofline.  `value` is the design's decode rate.
+
+`--workload hybrid`: the same comparison for the Vikupel design (layers in turn: rotary attention with
+unit-norm heads and turned values, a Mamba-2 mixer, windowed attention with a distance penalty and a
+gate, a Mamba-2 mixer; parallel blocks with a per-layer token input) beside a Llama of equal width,
+heads, feed-forward width and layers.
 
 Weights are random N(0, 0.02); token ids are uniform random from a seed.  No L2 flush is needed
 between steps: a step reads gigabytes of weights, far more than the 126 MB L2 holds.
@@ -175,8 +180,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--model", default="llama31-8b", choices=sorted(MODELS), help="layer sizes (random weights)")
     ap.add_argument("--dtype", default="bf16", choices=sorted(DTYPES), help="compute dtype; fp32 is the true 32-bit path")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent"])
-    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent: the layer sizes to compare at")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent", "hybrid"])
+    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent, hybrid: the layer sizes to compare at")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=None,
                     help="cached tokens per request of the headline point (default 8192 for llama31-8b, 4096 for "
@@ -197,6 +202,8 @@ def main():
         return serve(args)
     if args.workload == "latent":
         return latent(args)
+    if args.workload == "hybrid":
+        return latent(args, design="vikupel")
     return decode(args)
 
 
@@ -508,7 +515,36 @@ def latent_configs(size, layers, vocab=32000, window=4096, groups=8):
     return ours, llama
 
 
-def latent(args):
+# Vikupel at the same two widths: attention heads of 128 (a quarter as many KV heads), the recurrent
+# mixer twice as wide as the model with heads of 64 and a state of 128, a per-layer token input of 256.
+HYBRID_SIZES = {
+    "2b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ssm_heads=64, ssm_vdim=64, state=128, ff=5632, side=256),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, ssm_heads=128, ssm_vdim=64, state=128, ff=14336, side=256),
+}
+
+
+def hybrid_configs(size, layers, vocab=32000, window=1024):
+    """Layers in turn: rotary attention, recurrent, windowed attention, recurrent; and the Llama beside it."""
+    s = HYBRID_SIZES[size]
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5}
+    kinds = [{"type": "attention_2", "mixer": dict(att, rot={"base": 500000.0, "dims": s["dim"], "scaling": {
+                  "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})},
+             {"type": "mamba2", "mixer": {"heads": s["ssm_heads"], "vdim": s["ssm_vdim"], "state": s["state"], "groups": 1,
+                                          "norm_groups": 1, "conv": 4}},
+             {"type": "attention", "mixer": dict(att, mask={"size": window})},
+             {"type": "mamba2", "mixer": {"heads": s["ssm_heads"], "vdim": s["ssm_vdim"], "state": s["state"], "groups": 1,
+                                          "norm_groups": 1, "conv": 4}}]
+    ours = {"architecture": "Vikupel", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "token_side": {"dim": s["side"]},
+            "layers": [dict(kinds[i % 4], mlp={"kind": "dense", "ff": s["ff"]}) for i in range(layers)]}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": s["width"], "num_hidden_layers": layers,
+             "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": 128,
+             "intermediate_size": s["ff"], "vocab_size": vocab, "rope_theta": 500000.0, "max_position_embeddings": 4096,
+             "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+    return ours, llama
+
+
+def latent(args, design="ruperax"):
     """Prefill (one 2048-token prompt in one step) and decode (batch 8 at 2048 cached tokens) of the
     Ruperax design at real layer sizes beside a Llama of equal size, random weights, and per kernel
     the time of one such step with its bytes, flops and fraction of the measured roofline (from
@@ -531,7 +567,8 @@ def latent(args):
     gen = torch.Generator().manual_seed(0)
     out = {}
     with ClockSampler() as clk:
-        for name, cfgd in zip(("ruperax", "llama"), latent_configs(args.size, L)):
+        configs = latent_configs(args.size, L) if design == "ruperax" else hybrid_configs(args.size, L)
+        for name, cfgd in zip((design, "llama"), configs):
             arch = registry.lookup(registry.architecture_name(cfgd))
             cfg = arch.read_config(cfgd)
             model = arch.build(cfg, td, "cuda", max_positions=max_len)
@@ -604,16 +641,19 @@ def latent(args):
             del runner, cache, model
             gc.collect()
             torch.cuda.empty_cache()
-    ours = out["ruperax"]
-    line = {"metric": f"decode tok/s (Ruperax {args.size} layer sizes, {args.dtype}, batch {B}, context {ctx_len})",
+    ours = out[design]
+    title = {"ruperax": "Ruperax", "vikupel": "Vikupel"}[design]
+    sizes = LATENT_SIZES[args.size] if design == "ruperax" else HYBRID_SIZES[args.size]
+    line = {"metric": f"decode tok/s ({title} {args.size} layer sizes, {args.dtype}, batch {B}, context {ctx_len})",
             "value": ours["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": ours["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": args.dtype, "data": "synthetic", "impl": "ours",
-            "config": dict(LATENT_SIZES[args.size], model=f"Ruperax, {args.size} layer sizes, random weights", layers=L,
-                           global_batch=B, seq_len=ctx_len, prefill_tokens=T, window=4096, vocab=32000, page_size=page,
+            "config": dict(sizes, model=f"{title}, {args.size} layer sizes, random weights", layers=L,
+                           global_batch=B, seq_len=ctx_len, prefill_tokens=T, window=4096 if design == "ruperax" else 1024,
+                           vocab=32000, page_size=page,
                            parallelism="single GPU", l2="weights of a step exceed the L2 at these sizes"),
             "clocks": clk.summary(), "gpu_launches": int(ours["decode_launches_per_step"] * K), "peaks": pk,
-            "ruperax": ours, "llama_equal_size": out["llama"]}
+            design: ours, "llama_equal_size": out["llama"]}
     print(json.dumps(line))
     return 0
 

@@ -178,6 +178,46 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
     }
   };
 
+  // 16-bit rows with 8-byte alignment: the next tile's rows are fetched into registers before the
+  // current tile is worked on and go to shared memory (as float32) after it, so that their latency
+  // is hidden behind the arithmetic (float32 rows do the same with cp.async, without registers).
+  constexpr int LT = TK * (DP / 4) / (AG_WARPS * 32);
+  static_assert(TK * (DP / 4) % (AG_WARPS * 32) == 0, "a tile's 8-byte pieces divide among the threads");
+  const bool staged = sizeof(T) == 2 && vec_ok;
+  uint2 rk[LT], rv[LT];
+  auto fetch = [&](int n) {
+    if constexpr (sizeof(T) == 2) {
+      const int b = n & 1;
+#pragma unroll
+      for (int it = 0; it < LT; ++it) {
+        const int idx = threadIdx.x + it * AG_WARPS * 32;
+        const int j = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+        const long long off = sm_row[b * TK + j];
+        rk[it] = rv[it] = make_uint2(0u, 0u);
+        if (off >= 0 && d < D) {
+          rk[it] = *reinterpret_cast<const uint2*>(kv_plane + off + d);
+          rv[it] = *reinterpret_cast<const uint2*>(kv_plane + off + v_off + d);
+        }
+      }
+    }
+  };
+  auto stash = [&](int n) {
+    if constexpr (sizeof(T) == 2) {
+      const int b = n & 1;
+      float* const kb = sm_k + b * TK * KS;
+      float* const vb = sm_v + b * TK * DP;
+#pragma unroll
+      for (int it = 0; it < LT; ++it) {
+        const int idx = threadIdx.x + it * AG_WARPS * 32;
+        const int j = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+        const T* ek = reinterpret_cast<const T*>(&rk[it]);
+        const T* ev = reinterpret_cast<const T*>(&rv[it]);
+        *reinterpret_cast<float4*>(&kb[j * KS + d]) = make_float4(to_f32<T>(ek[0]), to_f32<T>(ek[1]), to_f32<T>(ek[2]), to_f32<T>(ek[3]));
+        *reinterpret_cast<float4*>(&vb[j * DP + d]) = make_float4(to_f32<T>(ev[0]), to_f32<T>(ev[1]), to_f32<T>(ev[2]), to_f32<T>(ev[3]));
+      }
+    }
+  };
+
   // the row's queries, zero past the head size and for heads the chunk does not have
   for (int idx = threadIdx.x; idx < AG_HEADS * (DP / 4); idx += AG_WARPS * 32) {
     const int g = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
@@ -199,7 +239,10 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
     const bool more = n + 1 < n_tiles;
     if (more) find_rows(n + 1);                // (its buffer was last read for tile n - 1, before the barrier that ended it)
     __syncthreads();
-    if (more) load_tile(n + 1);
+    if (more) {
+      if (staged) fetch(n + 1);
+      else load_tile(n + 1);
+    }
     ag_cp_async_commit();
     ag_cp_async_wait<1>();                     // everything but the newest group: tile n is there
     const bool have = lane < TK && sm_row[b * TK + lane] >= 0;
@@ -254,6 +297,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
 #pragma unroll
       for (int i = 0; i < DI; ++i) acc[i] = a[i];
     }
+    if (more && staged) stash(n + 1);          // (into the other buffer; the next iteration's barriers come before it is read)
   }
   ag_cp_async_wait<0>();
   if (warp >= nh) return;

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32)
 attention_finish_kernel(const float* __restrict__ o, int ldo, int n_tokens, const int* __restrict__ positions,
                         const float* __restrict__ cs_v, int v_pairing, int n_pos_v, const float* __restrict__ gate,
                         int ldg, T* __restrict__ out, int ldout, int Hq, int Dv, int Dp, int* __restrict__ err) {
+  pdl_launch();      // the product that follows may fetch its weights meanwhile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * AP_WARPS + warp;
   if (item >= (long long)n_tokens * Hq) return;

@@ -8,8 +8,7 @@
 //                    portion's first token comes from u, which is all zero before a sequence's first token.
 // mamba_conv_state:  u <- the last taps - 1 inputs after this portion (old rows move up when the portion
 //                    is shorter than that).  A launch of its own, so that nobody reads u while it changes.
-// mamba_scan:        per (request, head, p) one warp walks the portion's tokens in order; lane l holds
-//                    S[n] for n = l, l + 32, ...:
+// mamba_scan:        per (request, head) and 32 values of p one block walks the portion's tokens in order:
 //                      dt = softplus(dt_raw + dt_bias[h]);  S[n] <- exp(-exp(A_log[h]) dt) S[n] + dt B[n] x[p]
 //                      y[p] = sum_n S[n] C[n] + D[h] x[p]
 //                    The sum over n has one fixed tree, and the walk is token by token whatever the
@@ -18,7 +17,7 @@
 //                    root mean square and multiplied by the weight; out in the compute type.
 #include "common.cuh"
 
-constexpr int MS_WARPS = 8;
+constexpr int MS_TC = 32;        // tokens per chunk that the walk stages in shared memory
 constexpr int MS_MAX_TAPS = 16;
 
 __device__ __forceinline__ float ms_silu(float v) { return v / (1.f + expf(-v)); }
@@ -67,51 +66,163 @@ mamba_conv_state_kernel(const float* __restrict__ proj, int ldp, int off_xbc, in
     if (s < taps - 1) u[(size_t)s * C + c] = keep[s];
 }
 
-template <int NK>
-__global__ void __launch_bounds__(MS_WARPS * 32)
+// Shared memory of the walk for 4 * NQ >= N state elements per (head, p): two buffers of a chunk's
+// B and C rows (zero past N), x of the block's 32 p, step size and decay per token; one buffer of y.
+template <int NQ>
+struct MsTile {
+  static constexpr int W = 4 * NQ;
+  static constexpr int OFF_B = 0;
+  static constexpr int OFF_C = OFF_B + 2 * MS_TC * W;
+  static constexpr int OFF_X = OFF_C + 2 * MS_TC * W;
+  static constexpr int OFF_DT = OFF_X + 2 * MS_TC * 32;
+  static constexpr int OFF_DECAY = OFF_DT + 2 * MS_TC;
+  static constexpr int OFF_Y = OFF_DECAY + 2 * MS_TC;
+  static constexpr int SMEM_BYTES = (OFF_Y + MS_TC * 32) * 4;
+};
+
+__device__ __forceinline__ void ms_cp_async(void* smem, const void* gmem, int bytes, int src_bytes) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+
+// A block of four warps walks the tokens of one (request, head) for 32 values of p: lane = q * 8 + i
+// of warp w holds S[n] for p = 32 blockIdx.x + 8 w + i and n in [q NQ, (q + 1) NQ); the four q of a p
+// add their parts of y by two shuffles (one fixed tree).  The tokens' x, B, C arrive in chunks of
+// MS_TC through two shared-memory buffers (cp.async, the next chunk on its way while this one is
+// walked); step size and decay of a chunk's tokens are worked out by one thread per token, off the
+// serial chain, which is one fused multiply-add per state element and token.
+template <int NQ>
+__global__ void __launch_bounds__(128)
 mamba_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int off_dt,
                   const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
-                  const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int p = blockIdx.x * MS_WARPS + warp, h = blockIdx.y, r = blockIdx.z;
-  if (p >= P) return;
+                  const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups, int vec) {
+  using Tile = MsTile<NQ>;
+  constexpr int W = Tile::W;
+  extern __shared__ __align__(16) float ms_smem[];
+  float* const sB = ms_smem + Tile::OFF_B;
+  float* const sC = ms_smem + Tile::OFF_C;
+  float* const sX = ms_smem + Tile::OFF_X;
+  float* const sDt = ms_smem + Tile::OFF_DT;
+  float* const sDecay = ms_smem + Tile::OFF_DECAY;
+  float* const sY = ms_smem + Tile::OFF_Y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q = lane >> 3, pi = warp * 8 + (lane & 7);
+  const int p0 = blockIdx.x * 32, h = blockIdx.y, r = blockIdx.z;
+  const int p = p0 + pi;
   const int inner = heads * P;
   const int g = h / (heads / groups);
   const int t0 = q_start[r], t1 = q_start[r + 1];
-  float* S = state + (long long)slots[r] * state_stride + ((long long)h * P + p) * N;
-  float s[NK];
+  const int n_chunks = (t1 - t0 + MS_TC - 1) / MS_TC;
+  float* S = state + (long long)slots[r] * state_stride + ((long long)h * P + p) * N + q * NQ;
+  float s[NQ];
 #pragma unroll
-  for (int k = 0; k < NK; ++k) s[k] = lane + 32 * k < N ? S[lane + 32 * k] : 0.f;
+  for (int k = 0; k < NQ; ++k) s[k] = (p < P && q * NQ + k < N) ? S[k] : 0.f;
   const float a = expf(a_log[h]), db = dt_bias[h], dsk = d_skip[h];
   const int off_b = inner + g * N, off_c = inner + groups * N + g * N;
-#pragma unroll 2
-  for (int t = t0; t < t1; ++t) {
-    const float* row = xbc + (size_t)t * C;
-    const float dt = ms_softplus(proj[(size_t)t * ldp + off_dt + h] + db);
-    const float decay = expf(-a * dt);
-    const float x = row[h * P + p];
-    const float dtx = dt * x;
-    float acc = 0.f;
-#pragma unroll
-    for (int k = 0; k < NK; ++k) {
-      const int n = lane + 32 * k;
-      const float b = n < N ? row[off_b + n] : 0.f, c = n < N ? row[off_c + n] : 0.f;
-      s[k] = fmaf(decay, s[k], dtx * b);
-      acc = fmaf(s[k], c, acc);
+
+  auto stage = [&](int c, int b) {          // chunk c on its way into buffer b (the caller commits the group)
+    const int base = t0 + c * MS_TC;
+    const int cnt = min(MS_TC, t1 - base);          // (rows past the chunk's last token are never read)
+    if (vec) {
+      for (int idx = tid; idx < cnt * (W / 4); idx += 128) {
+        const int t = idx / (W / 4), n = (idx % (W / 4)) * 4;
+        const bool there = base + t < t1 && n < N;             // (N is a multiple of 4 here)
+        const float* row = xbc + (size_t)(there ? base + t : t0) * C;
+        ms_cp_async(&sB[(b * MS_TC + t) * W + n], row + off_b + (there ? n : 0), 16, there ? 16 : 0);
+        ms_cp_async(&sC[(b * MS_TC + t) * W + n], row + off_c + (there ? n : 0), 16, there ? 16 : 0);
+      }
+    } else {
+      for (int idx = tid; idx < cnt * W; idx += 128) {
+        const int t = idx / W, n = idx % W;
+        const bool there = base + t < t1 && n < N;
+        const float* row = xbc + (size_t)(there ? base + t : t0) * C;
+        ms_cp_async(&sB[(b * MS_TC + t) * W + n], row + off_b + (there ? n : 0), 4, there ? 4 : 0);
+        ms_cp_async(&sC[(b * MS_TC + t) * W + n], row + off_c + (there ? n : 0), 4, there ? 4 : 0);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) y[(size_t)t * inner + h * P + p] = fmaf(dsk, x, acc);
+    for (int idx = tid; idx < cnt * 32; idx += 128) {
+      const int t = idx >> 5, i = idx & 31;
+      const bool there = base + t < t1 && p0 + i < P;
+      ms_cp_async(&sX[(b * MS_TC + t) * 32 + i], xbc + (size_t)(there ? base + t : t0) * C + h * P + (there ? p0 + i : 0), 4,
+                  there ? 4 : 0);
+    }
+  };
+  auto raw_dt = [&](int c) {                // thread t: the step-size input of token t of chunk c
+    const int t = t0 + c * MS_TC + tid;
+    return (tid < MS_TC && t < t1) ? proj[(size_t)t * ldp + off_dt + h] : 0.f;
+  };
+  auto finish_dt = [&](float raw, int b) {
+    if (tid < MS_TC) {
+      const float dt = ms_softplus(raw + db);
+      sDt[b * MS_TC + tid] = dt;
+      sDecay[b * MS_TC + tid] = expf(-a * dt);
+    }
+  };
+
+  if (n_chunks > 0) {
+    stage(0, 0);
+    finish_dt(raw_dt(0), 0);
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int c = 0; c < n_chunks; ++c) {
+    const int b = c & 1;
+    const bool more = c + 1 < n_chunks;
+    float raw_next = 0.f;
+    if (more) {
+      stage(c + 1, b ^ 1);                  // (its buffer was last read for chunk c - 1, before the barrier that ended it)
+      raw_next = raw_dt(c + 1);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const int nt = min(MS_TC, t1 - t0 - c * MS_TC);
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t) {
+      const float decay = sDecay[b * MS_TC + t], dt = sDt[b * MS_TC + t];
+      const float x = sX[(b * MS_TC + t) * 32 + pi];
+      const float dtx = dt * x;
+      const float4* bp = reinterpret_cast<const float4*>(&sB[(b * MS_TC + t) * W + q * NQ]);
+      const float4* cp = reinterpret_cast<const float4*>(&sC[(b * MS_TC + t) * W + q * NQ]);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;      // four chains, added in one fixed order
 #pragma unroll
-  for (int k = 0; k < NK; ++k)
-    if (lane + 32 * k < N) S[lane + 32 * k] = s[k];
+      for (int k4 = 0; k4 < NQ / 4; ++k4) {
+        const float4 bb = bp[k4], cc = cp[k4];
+        s[4 * k4 + 0] = fmaf(decay, s[4 * k4 + 0], dtx * bb.x);
+        a0 = fmaf(s[4 * k4 + 0], cc.x, a0);
+        s[4 * k4 + 1] = fmaf(decay, s[4 * k4 + 1], dtx * bb.y);
+        a1 = fmaf(s[4 * k4 + 1], cc.y, a1);
+        s[4 * k4 + 2] = fmaf(decay, s[4 * k4 + 2], dtx * bb.z);
+        a2 = fmaf(s[4 * k4 + 2], cc.z, a2);
+        s[4 * k4 + 3] = fmaf(decay, s[4 * k4 + 3], dtx * bb.w);
+        a3 = fmaf(s[4 * k4 + 3], cc.w, a3);
+      }
+      float acc = (a0 + a1) + (a2 + a3);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+      if (q == 0) sY[t * 32 + pi] = fmaf(dsk, x, acc);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nt * 32; idx += 128) {
+      const int t = idx >> 5, i = idx & 31;
+      if (p0 + i < P) y[(size_t)(t0 + c * MS_TC + t) * inner + h * P + p0 + i] = sY[idx];
+    }
+    if (more) finish_dt(raw_next, b ^ 1);
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (p < P) {
+#pragma unroll
+    for (int k = 0; k < NQ; ++k)
+      if (q * NQ + k < N) S[k] = s[k];
+  }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 mamba_gate_norm_kernel(const float* __restrict__ y, int inner, const float* __restrict__ proj, int ldp, int off_z,
                        const float* __restrict__ w, T* __restrict__ out, int ldo, int norm_groups, float eps) {
+  pdl_launch();      // the product that follows may fetch its weights meanwhile
   __shared__ float red[32];
   const int t = blockIdx.x, grp = blockIdx.y;
   const int width = inner / norm_groups;
@@ -162,14 +273,27 @@ FERRUM_API int ferrum_mamba2_mix(const float* proj, int ldp, int n_tokens, int n
     FERRUM_CHECK_LAUNCH("mamba_conv_state");
   }
   {
-    const dim3 grid((P + MS_WARPS - 1) / MS_WARPS, heads, n_reqs);
-#define MS_SCAN(NK_)                                                                                                   \
-  mamba_scan_kernel<NK_><<<grid, MS_WARPS * 32, 0, stream>>>(xbc, C, proj, ldp, off_dt, dt_bias, a_log, d_skip, state, \
-                                                            state_stride, q_start, slots, y, heads, P, N, groups)
-    if (N <= 32) MS_SCAN(1);
-    else if (N <= 64) MS_SCAN(2);
-    else if (N <= 128) MS_SCAN(4);
-    else MS_SCAN(8);
+    const dim3 grid((P + 31) / 32, heads, n_reqs);
+    // rows of B and C start on 16-byte borders: 16-byte copies
+    const int vec = N % 4 == 0 && C % 4 == 0 && inner % 4 == 0 && ((uintptr_t)xbc & 15) == 0;
+#define MS_SCAN(NQ_)                                                                                                       \
+  do {                                                                                                                     \
+    static bool configured = false;                                                                                        \
+    if (!configured) {                                                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(mamba_scan_kernel<NQ_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                           MsTile<NQ_>::SMEM_BYTES);                                                       \
+      FERRUM_CHECK_ARG(e == cudaSuccess, "mamba2: cannot reserve %d bytes of shared memory: %s", MsTile<NQ_>::SMEM_BYTES,  \
+                       cudaGetErrorString(e));                                                                             \
+      configured = true;                                                                                                   \
+    }                                                                                                                      \
+    mamba_scan_kernel<NQ_><<<grid, 128, MsTile<NQ_>::SMEM_BYTES, stream>>>(xbc, C, proj, ldp, off_dt, dt_bias, a_log, d_skip, \
+                                                                          state, state_stride, q_start, slots, y, heads, P, N, \
+                                                                          groups, vec);                                    \
+  } while (0)
+    if (N <= 32) MS_SCAN(8);
+    else if (N <= 64) MS_SCAN(16);
+    else if (N <= 128) MS_SCAN(32);
+    else MS_SCAN(64);
 #undef MS_SCAN
     FERRUM_CHECK_LAUNCH("mamba_scan");
   }

@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 10
+ABI = 11
 
 
 def lib():
@@ -814,34 +814,57 @@ def mamba2_mix(proj, n_tokens, ctx, conv_w, conv_b, dt_bias, a_log, d_skip, norm
 
 
 # ----------------------------------------------------------------------------- parallel block
-def scaled_sum(x, y1, y2, mult, n_tokens, xc=None):
+def _partials_args(p):
+    return (_ptr(p.workspace), p._c) if p is not None else (c_void_p(0), None)
+
+
+def scaled_sum(x, y1, y2, mult, n_tokens, xc=None, p1=None, p2=None):
     """x[:n] += mult * (y1 + y2) in float32 (y2 may be None); xc, when given, also receives the new rows
-    in its own type."""
-    _need(x, torch.float32, "x", 2); _need(y1, torch.float32, "y1", 2)
+    in its own type.  p1 / p2 (`Partials`) stand in for y1 / y2 when the sublayers left their last
+    products in deferred mode."""
+    _need(x, torch.float32, "x", 2)
     E = x.shape[1]
-    ok = x.is_contiguous() and y1.is_contiguous() and y1.shape[1] == E and (y2 is None or (y2.is_contiguous() and y2.shape[1] == E))
-    if not ok or (xc is not None and (not xc.is_contiguous() or xc.shape[1] != E)):
+    for y, p in ((y1, p1), (y2, p2)):
+        if p is None and y is not None:
+            _need(y, torch.float32, "y", 2)
+            if not y.is_contiguous() or y.shape[1] != E:
+                raise KernelError("scaled_sum: rows must be contiguous and of one width")
+    if (y1 is None and p1 is None) or not x.is_contiguous() or (xc is not None and (not xc.is_contiguous() or xc.shape[1] != E)):
         raise KernelError("scaled_sum: rows must be contiguous and of one width")
     _bytes_work((x, 2 * n_tokens), (y1, n_tokens), (y2, n_tokens), (xc, n_tokens))
-    _check(lib().ferrum_scaled_sum(_ptr(x), _ptr(y1), _ptr(y2), c_float(mult), _ptr(xc),
-                                   dtype_code(xc.dtype if xc is not None else torch.float32), c_int(n_tokens), c_int(E), _stream()),
-           "scaled_sum")
+    _check(lib().ferrum_scaled_sum(_ptr(x), _ptr(y1 if p1 is None else None), _ptr(y2 if p2 is None else None), c_float(mult),
+                                   _ptr(xc), dtype_code(xc.dtype if xc is not None else torch.float32), c_int(n_tokens), c_int(E),
+                                   *_partials_args(p1), *_partials_args(p2), _stream()), "scaled_sum")
 
 
-def gated_table_rows(s, table, token_ids, offset, dim, out, n_tokens, err):
-    """out[t, j] = gelu_tanh(s[t, j]) * table[token_ids[t], offset + j]; s float32, table and out in the compute type."""
-    _need(s, torch.float32, "s", 2); _need(table, out.dtype, "table", 2); _need(token_ids, torch.int32, "token_ids", 1)
-    _check(lib().ferrum_gated_table_rows(_ptr(s), c_int(s.stride(0)), _ptr(table), c_int(table.stride(0)), c_int(table.shape[0]),
+def gated_table_rows(s, table, token_ids, offset, dim, out, n_tokens, err, partials=None):
+    """out[t, j] = gelu_tanh(s[t, j]) * table[token_ids[t], offset + j]; s float32 (or a deferred product,
+    `partials`), table and out in the compute type."""
+    _need(table, out.dtype, "table", 2); _need(token_ids, torch.int32, "token_ids", 1)
+    if partials is None:
+        _need(s, torch.float32, "s", 2)
+    _check(lib().ferrum_gated_table_rows(_ptr(s if partials is None else None), c_int(s.stride(0) if partials is None else 0),
+                                         _ptr(table), c_int(table.stride(0)), c_int(table.shape[0]),
                                          _ptr(token_ids), c_int(offset), c_int(dim), _ptr(out), c_int(out.stride(0)),
-                                         dtype_code(out.dtype), c_int(n_tokens), _ptr(err), _stream()), "gated_table_rows")
+                                         dtype_code(out.dtype), c_int(n_tokens), _ptr(err), *_partials_args(partials), _stream()),
+           "gated_table_rows")
 
 
-def norm_scaled_add(x, y, w, mult, eps, n_tokens):
-    """x[:n] += mult * y / sqrt(mean(y^2) + eps) * w, all float32."""
-    _need(x, torch.float32, "x", 2); _need(y, torch.float32, "y", 2); _need(w, torch.float32, "w", 1)
+def norm_scaled_add_max_width():
+    """The widest row whose product `norm_scaled_add` can take as partials."""
+    return int(lib().ferrum_norm_scaled_add_max_width())
+
+
+def norm_scaled_add(x, y, w, mult, eps, n_tokens, partials=None):
+    """x[:n] += mult * y / sqrt(mean(y^2) + eps) * w, all float32; y a buffer or a deferred product (`partials`)."""
+    _need(x, torch.float32, "x", 2); _need(w, torch.float32, "w", 1)
     E = x.shape[1]
-    if y.shape[1] != E or w.shape[0] != E or not x.is_contiguous() or not y.is_contiguous():
+    if partials is None:
+        _need(y, torch.float32, "y", 2)
+        if y.shape[1] != E or not y.is_contiguous():
+            raise KernelError("norm_scaled_add: shapes do not agree")
+    if w.shape[0] != E or not x.is_contiguous():
         raise KernelError("norm_scaled_add: shapes do not agree")
-    _bytes_work((x, 2 * n_tokens), (y, n_tokens))
-    _check(lib().ferrum_norm_scaled_add(_ptr(x), _ptr(y), _ptr(w), c_float(mult), c_float(eps), c_int(n_tokens), c_int(E), _stream()),
-           "norm_scaled_add")
+    _bytes_work((x, 2 * n_tokens), (x, n_tokens))
+    _check(lib().ferrum_norm_scaled_add(_ptr(x), _ptr(y if partials is None else None), _ptr(w), c_float(mult), c_float(eps),
+                                        c_int(n_tokens), c_int(E), *_partials_args(partials), _stream()), "norm_scaled_add")

@@ -9,7 +9,7 @@ import torch
 
 from ..ops import lib as ops
 from .base import CacheNeed, FeedForward, Mixer, Norm, ParamSpec, Part, StateNeed
-from .linear import STORE_F32, linear
+from .linear import STORE_F32, linear, linear_deferred
 
 
 class PreNormBlock(Part):
@@ -189,13 +189,18 @@ class TokenSideInput(Part):
     def forward(self, h, x_in, ctx, mult):
         """h: the float32 residual rows (updated in place); x_in: the same rows in the compute type."""
         T, cap = ctx.n_tokens, ctx.token_capacity
+        few = T <= OVERLAP_MAX_TOKENS       # a few tokens: both products stay in partials, summed by the kernels that follow
         s = ctx.buf("side_s", (cap, self.dim), torch.float32)
-        linear(x_in, self.w_gate_weight, s, STORE_F32, ctx, M=T)
+        part = linear_deferred(x_in, self.w_gate_weight, ctx, T) if few else None
+        if part is None:
+            linear(x_in, self.w_gate_weight, s, STORE_F32, ctx, M=T)
         g = ctx.buf("side_g", (cap, self.dim), self.dtype)
-        ops.gated_table_rows(s, self.table.w_weight, ctx.token_ids, self.offset, self.dim, g, T, ctx.err)
+        ops.gated_table_rows(s, self.table.w_weight, ctx.token_ids, self.offset, self.dim, g, T, ctx.err, partials=part)
         y = ctx.buf("side_y", (cap, self.width), torch.float32)
-        linear(g, self.w_proj_weight, y, STORE_F32, ctx, M=T)
-        ops.norm_scaled_add(h, y, self.w_norm_weight, mult, self.eps, T)
+        part = linear_deferred(g, self.w_proj_weight, ctx, T) if few and self.width <= ops.norm_scaled_add_max_width() else None
+        if part is None:
+            linear(g, self.w_proj_weight, y, STORE_F32, ctx, M=T)
+        ops.norm_scaled_add(h, y, self.w_norm_weight, mult, self.eps, T, partials=part)
 
 
 class ParallelBlock(Part):
@@ -227,15 +232,36 @@ class ParallelBlock(Part):
         x = self.norm1.forward(h, ctx)
         ctx.flush_residual()
         y1 = ctx.buf("par_y1", (cap, E), torch.float32)
-        self.mixer.forward(x, ctx, cache, y1, accumulate=False)
-        y2 = None
-        if self.ffn is not None:
-            y2 = ctx.buf("par_y2", (cap, E), torch.float32)
-            self.ffn.forward(x, ctx, y2, accumulate=False)
+        y2 = ctx.buf("par_y2", (cap, E), torch.float32) if self.ffn is not None else None
+        p1 = p2 = None
+        # The mixer and the feed-forward read the same rows and meet only in the sum.  In steps of a few
+        # tokens every kernel of a chain waits for the one before it far longer than it computes: the
+        # feed-forward runs on a second stream beside the mixer (products there use the second lane's
+        # workspace), and each chain's last product may stay in partials that the sum adds.
+        if self.ffn is not None and T <= OVERLAP_MAX_TOKENS and not ops.profiling() and str(ctx.device) != "cpu":
+            side, fork, join = ctx.side_stream()
+            main = torch.cuda.current_stream()
+            fork.record(main)
+            side.wait_event(fork)
+            ctx.lane = 1
+            try:
+                with torch.cuda.stream(side):
+                    p2 = self.ffn.forward(x, ctx, y2, accumulate=False, defer=True)
+                    join.record(side)
+            finally:
+                ctx.lane = 0
+            p1 = self.mixer.forward(x, ctx, cache, y1, accumulate=False, defer=True)
+            main.wait_event(join)
+        else:
+            few = T <= OVERLAP_MAX_TOKENS       # (one workspace: only the last product before the sum may stay in partials)
+            p1 = self.mixer.forward(x, ctx, cache, y1, accumulate=False, defer=few and self.ffn is None)
+            if self.ffn is not None:
+                ctx.flush_residual()
+                p2 = self.ffn.forward(x, ctx, y2, accumulate=False, defer=few)
         ctx.flush_residual()
         xc = None
         if self.side is not None and self.side.dtype != torch.float32:
             xc = ctx.buf("par_xc", (cap, E), self.side.dtype)
-        ops.scaled_sum(h, y1, y2, self.mult, T, xc)
+        ops.scaled_sum(h, y1, y2, self.mult, T, xc, p1=p1, p2=p2)
         if self.side is not None:
             self.side.forward(h, xc if xc is not None else h, ctx, self.mult)

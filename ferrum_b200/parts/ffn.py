@@ -81,10 +81,6 @@ class SwiGLU(FeedForward):
                 linear(x, self.w_gate_up, gu, STORE_F32, ctx, M=T)
                 self.extra_out = gu[:, 2 * F:] if n > 2 * F else None
                 ops.bias_glu(gu, self.w_gate_bias, self.w_up_bias, act, T, F, self.act)
-            if defer and not accumulate:
-                part = linear_deferred(act, self.w_down_weight, ctx, T)
-                if part is not None:
-                    return part
         elif ops.gemm_tc_supported(x, self.w_gate_up):
             linear_swiglu(x, self.w_gate_up, act, F, ctx, M=T)
         elif self.wide_products and self.dtype != torch.float32:
@@ -95,5 +91,9 @@ class SwiGLU(FeedForward):
             gu = ctx.buf("ffn_gate_up", (ctx.token_capacity, 2 * F), self.dtype)
             linear(x, self.w_gate_up, gu, STORE, ctx, M=T)
             ops.swiglu(gu, act, T, F)
+        if defer and not accumulate:
+            part = linear_deferred(act, self.w_down_weight, ctx, T)
+            if part is not None:
+                return part
         linear(act, self.w_down_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
         return None

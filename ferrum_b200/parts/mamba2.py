@@ -22,7 +22,7 @@ import torch
 
 from ..ops import lib as ops
 from .base import CacheNeed, Mixer, ParamSpec, StateNeed
-from .linear import RESIDUAL, STORE_F32, linear
+from .linear import RESIDUAL, STORE_F32, linear, linear_deferred
 
 
 def _draw_a_log(shape, g, device, std):
@@ -74,5 +74,9 @@ class Mamba2Mixer(Mixer):
         out = ctx.buf("ssm_out", (cap, self.inner), self.dtype)
         ops.mamba2_mix(proj, T, ctx, self.w_conv_weight, self.w_conv_bias, self.w_dt_bias, self.w_A_log, self.w_D,
                        self.w_norm_weight, self.H, self.P, self.N, self.G, self.norm_groups, self.eps, cache.state, xbc, y, out)
+        if defer and not accumulate:
+            part = linear_deferred(out, self.w_o_weight, ctx, T)
+            if part is not None:
+                return part
         linear(out, self.w_o_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
         return None

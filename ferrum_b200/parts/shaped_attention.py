@@ -26,7 +26,7 @@ import torch
 from ..ops import lib as ops
 from .attention import PagedAttention
 from .base import CacheNeed, PagedKVNeed, ParamSpec
-from .linear import RESIDUAL, STORE_F32, linear
+from .linear import RESIDUAL, STORE_F32, linear, linear_deferred
 
 
 class ShapedAttention(PagedAttention):
@@ -85,5 +85,9 @@ class ShapedAttention(PagedAttention):
         gate = proj[:, off:off + Hq * Dv] if self.has_gate else None
         ops.attention_finish(o, T, ctx, vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0,
                              gate, out, Hq, Dv, Dp)
+        if defer and not accumulate:
+            part = linear_deferred(out, self.w_output_weight, ctx, T)
+            if part is not None:
+                return part
         linear(out, self.w_output_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
         return None

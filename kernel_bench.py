@@ -9,6 +9,8 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py gemm|attn_decode|attn_prefill ... --dtype fp32    (the CUDA-core kernels of the 32-bit path)
     python kernel_bench.py latent_decode|latent_prefill [--hq 16] [--kv-rank 512] [--rot-dim 64] [--window W] [--cuda-cores]
     python kernel_bench.py head_linear --tokens 8 --hq 16 --n 512 --k 128
+    python kernel_bench.py attn_decode|attn_prefill --exact [--window W] [--penalty]   (float32 weights and sums on 16-bit storage)
+    python kernel_bench.py ssm --tokens 2048 [--batch 1] [--hq 64] [--head-dim 64] [--state 128]   (the state-space mixer's kernels)
     python kernel_bench.py rmsnorm|rope --tokens 8
     python kernel_bench.py step --tokens 2048 [--layers 2] [--dtype bf16|fp16|fp32]   (one prompt portion through the model)
     FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
@@ -34,12 +36,15 @@ sys.path.insert(0, ROOT)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "latent_decode", "latent_prefill", "head_linear", "gemm", "rmsnorm",
-                                       "rope", "step", "timeline"])
+                                       "rope", "ssm", "step", "timeline"])
     ap.add_argument("--kv-rank", type=int, default=512, help="latent_*: elements of the cached latent (the values)")
     ap.add_argument("--rot-dim", type=int, default=64, help="latent_*: rotated key elements behind the latent")
     ap.add_argument("--window", type=int, default=0, help="latent_*: keys a query looks back over (0: all)")
     ap.add_argument("--stage", type=int, default=0, choices=[0, 32, 64], help="latent_*: force the tensor-core kernel's stage size")
     ap.add_argument("--cuda-cores", action="store_true", help="latent_*: the CUDA-core kernel also where the tensor-core one applies")
+    ap.add_argument("--exact", action="store_true", help="attn_*: the CUDA-core kernel with float32 results, as the shaped attention runs it")
+    ap.add_argument("--penalty", action="store_true", help="attn_* --exact: with a distance penalty per head")
+    ap.add_argument("--state", type=int, default=128, help="ssm: state elements per head and value element")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=8)
@@ -115,9 +120,30 @@ def main():
         table = ctx.block_tables[0]
         run_attention = att._flash if ops.attention_flash_supported(td, D) else att._generic
         runs = [lambda c=c: run_attention(q, out, ctx, c, table) for c in caches]
+        if args.exact:
+            att.window = args.window
+            out32 = torch.empty(T, Hq * D, device=dev, dtype=torch.float32)
+            pen = (torch.rand(Hq, device=dev), torch.rand(Hq, device=dev)) if args.penalty else None
+            runs = [lambda c=c: att._generic(q, out32, ctx, c, table, pen) for c in caches]
         kv_bytes = R * ctx_len * 2 * Hkv * D * esize
         flops = 4.0 * Hq * D * (ctx_len * qlen if decode else qlen * qlen / 2) * R
         work = {"bytes": kv_bytes + 2 * T * Hq * D * esize, "flops": flops, "bound": "hbm" if decode else "tensor"}
+    elif args.kernel == "ssm":
+        # --batch requests of --tokens tokens each; --hq heads of --head-dim elements, one group
+        H, P, N, R, n = Hq, D, args.state, args.batch, args.tokens
+        inner, C, T = H * P, H * P + 2 * N, args.batch * args.tokens
+        ctx = StepContext(dev, max(16, T), R, [])
+        ctx.fill([StepEntry(r, 0, [1] * n) for r in range(R)], [])
+        proj = torch.randn(T, 2 * inner + 2 * N + H, device=dev, generator=gen)
+        f = lambda *shape: torch.randn(*shape, device=dev, generator=gen) * 0.2
+        conv_w, conv_b, dt_bias, a_log, d_skip, norm_w = f(C, 4), f(C), f(H), f(H), f(H), f(inner)
+        states = [torch.zeros(R, inner * N + 3 * C, device=dev) for _ in range(args.layers)]
+        xbc, y = torch.empty(T, C, device=dev), torch.empty(T, inner, device=dev)
+        out = torch.empty(T, inner, device=dev, dtype=td)
+        runs = [lambda st=st: ops.mamba2_mix(proj, T, ctx, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w, H, P, N, 1, 1, 1e-6, st,
+                                             xbc, y, out) for st in states]
+        work = {"bytes": T * 4 * (inner + 2 * C + H + 3 * inner) + T * inner * esize + 2 * R * inner * N * 4,
+                "flops": 6.0 * T * inner * N, "bound": "ffma"}
     elif args.kernel in ("latent_decode", "latent_prefill"):
         # attention over cached rows of kv_rank + rot_dim elements, --hq heads sharing them
         decode = args.kernel == "latent_decode"
@@ -233,7 +259,7 @@ def main():
     tf = work["flops"] / (us * 1e-6) / 1e12
     if work["bound"] == "hbm":
         frac = gbs / pk["hbm_gbs"]
-    elif args.dtype == "fp32":       # the CUDA cores' own peak: SMs x 128 lanes x 2 flops x the maximum clock
+    elif args.dtype == "fp32" or work["bound"] == "ffma" or args.exact:       # the CUDA cores' own peak: SMs x 128 lanes x 2 flops x the maximum clock
         frac = tf / (ops.sm_count() * 128 * 2 * 1.965e9 / 1e12)
         work["bound"] = "ffma"
     else:

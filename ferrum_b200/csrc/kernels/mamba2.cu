@@ -66,11 +66,11 @@ mamba_conv_state_kernel(const float* __restrict__ proj, int ldp, int off_xbc, in
     if (s < taps - 1) u[(size_t)s * C + c] = keep[s];
 }
 
-// Shared memory of the walk for 4 * NQ >= N state elements per (head, p): two buffers of a chunk's
+// Shared memory of the walk for 16 * NQ >= N state elements per (head, p): two buffers of a chunk's
 // B and C rows (zero past N), x of the block's 32 p, step size and decay per token; one buffer of y.
 template <int NQ>
 struct MsTile {
-  static constexpr int W = 4 * NQ;
+  static constexpr int W = 16 * NQ;
   static constexpr int OFF_B = 0;
   static constexpr int OFF_C = OFF_B + 2 * MS_TC * W;
   static constexpr int OFF_X = OFF_C + 2 * MS_TC * W;
@@ -86,12 +86,14 @@ __device__ __forceinline__ void ms_cp_async(void* smem, const void* gmem, int by
   else asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
 }
 
-// A block of four warps walks the tokens of one (request, head) for 32 values of p: lane = q * 8 + i
-// of warp w holds S[n] for p = 32 blockIdx.x + 8 w + i and n in [q NQ, (q + 1) NQ); the four q of a p
-// add their parts of y by two shuffles (one fixed tree).  The tokens' x, B, C arrive in chunks of
-// MS_TC through two shared-memory buffers (cp.async, the next chunk on its way while this one is
-// walked); step size and decay of a chunk's tokens are worked out by one thread per token, off the
-// serial chain, which is one fused multiply-add per state element and token.
+// A block of four warps walks the tokens of one (request, head) for 32 values of p.  Lane = g * 16 + q
+// of warp w holds S[n] for the four p = 32 blockIdx.x + 8 w + 4 g + j and n in [q NQ, (q + 1) NQ): a
+// token's B and C values are read from shared memory once for four p (the walk is bound by what shared
+// memory delivers otherwise), and the sixteen q of a p add their parts of y in one fixed tree of five
+// shuffles that carries the four p together.  The tokens' x, B, C arrive in chunks of MS_TC through two
+// shared-memory buffers (cp.async, the next chunk on its way while this one is walked); step size and
+// decay of a chunk's tokens are worked out by one thread per token, off the serial chain, which is one
+// fused multiply-add per state element and token.
 template <int NQ>
 __global__ void __launch_bounds__(128)
 mamba_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int ldp, int off_dt,
@@ -108,17 +110,19 @@ mamba_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict_
   float* const sDecay = ms_smem + Tile::OFF_DECAY;
   float* const sY = ms_smem + Tile::OFF_Y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q = lane >> 3, pi = warp * 8 + (lane & 7);
+  const int q = lane & 15, pi = warp * 8 + (lane >> 4) * 4;     // pi: the first of this lane's four p within the block
   const int p0 = blockIdx.x * 32, h = blockIdx.y, r = blockIdx.z;
   const int p = p0 + pi;
   const int inner = heads * P;
   const int g = h / (heads / groups);
   const int t0 = q_start[r], t1 = q_start[r + 1];
   const int n_chunks = (t1 - t0 + MS_TC - 1) / MS_TC;
-  float* S = state + (long long)slots[r] * state_stride + ((long long)h * P + p) * N + q * NQ;
-  float s[NQ];
+  float* S = state + (long long)slots[r] * state_stride + ((long long)h * P + p) * N + q * NQ;     // (p + j: N further each)
+  float s[4][NQ];
 #pragma unroll
-  for (int k = 0; k < NQ; ++k) s[k] = (p < P && q * NQ + k < N) ? S[k] : 0.f;
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int k = 0; k < NQ; ++k) s[j][k] = (p + j < P && q * NQ + k < N) ? S[(long long)j * N + k] : 0.f;
   const float a = expf(a_log[h]), db = dt_bias[h], dsk = d_skip[h];
   const int off_b = inner + g * N, off_c = inner + groups * N + g * N;
 
@@ -178,30 +182,59 @@ mamba_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict_
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
     const int nt = min(MS_TC, t1 - t0 - c * MS_TC);
-#pragma unroll 2
-    for (int t = 0; t < nt; ++t) {
-      const float decay = sDecay[b * MS_TC + t], dt = sDt[b * MS_TC + t];
-      const float x = sX[(b * MS_TC + t) * 32 + pi];
-      const float dtx = dt * x;
-      const float4* bp = reinterpret_cast<const float4*>(&sB[(b * MS_TC + t) * W + q * NQ]);
-      const float4* cp = reinterpret_cast<const float4*>(&sC[(b * MS_TC + t) * W + q * NQ]);
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;      // four chains, added in one fixed order
+    // Four tokens at a time: their state updates follow each other (one fused multiply-add deep per
+    // token and state element), and the 16 parts of y (4 tokens x 4 p) of a lane meet those of the
+    // other fifteen q in ONE tree of four exchanges that halves what a lane carries at every step, so
+    // that lane q ends with the sum for token q / 4 and p q % 4.
+    for (int t4 = 0; t4 < nt; t4 += 4) {
+      float a[16];
 #pragma unroll
-      for (int k4 = 0; k4 < NQ / 4; ++k4) {
-        const float4 bb = bp[k4], cc = cp[k4];
-        s[4 * k4 + 0] = fmaf(decay, s[4 * k4 + 0], dtx * bb.x);
-        a0 = fmaf(s[4 * k4 + 0], cc.x, a0);
-        s[4 * k4 + 1] = fmaf(decay, s[4 * k4 + 1], dtx * bb.y);
-        a1 = fmaf(s[4 * k4 + 1], cc.y, a1);
-        s[4 * k4 + 2] = fmaf(decay, s[4 * k4 + 2], dtx * bb.z);
-        a2 = fmaf(s[4 * k4 + 2], cc.z, a2);
-        s[4 * k4 + 3] = fmaf(decay, s[4 * k4 + 3], dtx * bb.w);
-        a3 = fmaf(s[4 * k4 + 3], cc.w, a3);
+      for (int tt = 0; tt < 4; ++tt) {
+        if (t4 + tt < nt) {                              // (the same for the whole block)
+          const int t = t4 + tt;
+          const float decay = sDecay[b * MS_TC + t], dt = sDt[b * MS_TC + t];
+          const float4 x4 = *reinterpret_cast<const float4*>(&sX[(b * MS_TC + t) * 32 + pi]);
+          const float x[4] = {x4.x * dt, x4.y * dt, x4.z * dt, x4.w * dt};
+          const float4* bp = reinterpret_cast<const float4*>(&sB[(b * MS_TC + t) * W + q * NQ]);
+          const float4* cp = reinterpret_cast<const float4*>(&sC[(b * MS_TC + t) * W + q * NQ]);
+          float bv[NQ], cv[NQ];
+#pragma unroll
+          for (int k4 = 0; k4 < NQ / 4; ++k4) {
+            const float4 bb = bp[k4], cc = cp[k4];
+            bv[4 * k4] = bb.x; bv[4 * k4 + 1] = bb.y; bv[4 * k4 + 2] = bb.z; bv[4 * k4 + 3] = bb.w;
+            cv[4 * k4] = cc.x; cv[4 * k4 + 1] = cc.y; cv[4 * k4 + 2] = cc.z; cv[4 * k4 + 3] = cc.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float a0 = 0.f, a1 = 0.f;                    // two chains, added in one fixed order
+#pragma unroll
+            for (int k = 0; k < NQ; k += 2) {
+              s[j][k] = fmaf(decay, s[j][k], bv[k] * x[j]);
+              a0 = fmaf(s[j][k], cv[k], a0);
+              s[j][k + 1] = fmaf(decay, s[j][k + 1], bv[k + 1] * x[j]);
+              a1 = fmaf(s[j][k + 1], cv[k + 1], a1);
+            }
+            a[tt * 4 + j] = a0 + a1;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a[tt * 4 + j] = 0.f;
+        }
       }
-      float acc = (a0 + a1) + (a2 + a3);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-      if (q == 0) sY[t * 32 + pi] = fmaf(dsk, x, acc);
+#pragma unroll
+      for (int half = 8; half >= 1; half >>= 1) {        // exchange with lane q ^ half; keep the half of the values that q's bit names
+        const bool hi = (q & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+          const float keep = hi ? a[i + half] : a[i], send = hi ? a[i] : a[i + half];
+          a[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+      }
+      const int tt = q >> 2, j = q & 3;
+      if (t4 + tt < nt) {
+        const int t = t4 + tt;
+        sY[t * 32 + pi + j] = fmaf(dsk, sX[(b * MS_TC + t) * 32 + pi + j], a[0]);
+      }
     }
     __syncthreads();
     for (int idx = tid; idx < nt * 32; idx += 128) {
@@ -211,11 +244,11 @@ mamba_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict_
     if (more) finish_dt(raw_next, b ^ 1);
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if (p < P) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
 #pragma unroll
     for (int k = 0; k < NQ; ++k)
-      if (q * NQ + k < N) S[k] = s[k];
-  }
+      if (p + j < P && q * NQ + k < N) S[(long long)j * N + k] = s[j][k];
 }
 
 template <typename T>
@@ -290,10 +323,9 @@ FERRUM_API int ferrum_mamba2_mix(const float* proj, int ldp, int n_tokens, int n
                                                                           state, state_stride, q_start, slots, y, heads, P, N, \
                                                                           groups, vec);                                    \
   } while (0)
-    if (N <= 32) MS_SCAN(8);
-    else if (N <= 64) MS_SCAN(16);
-    else if (N <= 128) MS_SCAN(32);
-    else MS_SCAN(64);
+    if (N <= 64) MS_SCAN(4);
+    else if (N <= 128) MS_SCAN(8);
+    else MS_SCAN(16);
 #undef MS_SCAN
     FERRUM_CHECK_LAUNCH("mamba_scan");
   }

@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 11
+ABI = 12
 
 
 def lib():
@@ -809,7 +809,8 @@ def mamba2_mix(proj, n_tokens, ctx, conv_w, conv_b, dt_bias, a_log, d_skip, norm
                                    _ptr(ctx.q_start), _ptr(ctx.slots), _ptr(conv_w), _ptr(conv_b), c_int(taps), _ptr(dt_bias),
                                    _ptr(a_log), _ptr(d_skip), _ptr(norm_w), c_int(heads), c_int(P), c_int(N), c_int(groups),
                                    c_int(norm_groups), c_float(eps), _ptr(state), c_longlong(state.stride(0)), _ptr(xbc), _ptr(y),
-                                   _ptr(out), c_int(out.stride(0)), dtype_code(out.dtype), _stream()), "mamba2_mix")
+                                   _ptr(out), c_int(out.stride(0)), dtype_code(out.dtype), c_int(ctx.max_q_len), _stream()),
+           "mamba2_mix")
     launches += 3 if taps > 1 else 2       # (the entry point launches the convolution, its state, the walk and the norm)
 
 

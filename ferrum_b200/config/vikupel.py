@@ -9,11 +9,11 @@ models of the design is read here and nowhere else.
 
 Mixers:
   `attention`    heads, kv_heads, dim, vdim, scale, mask.size (a query sees itself and the
-                 mask.size - 1 keys before it); a distance penalty and an output gate (their numbers
-                 are tensors).
+                 mask.size - 1 keys before it; no `mask`: every earlier key); a distance penalty and
+                 an output gate (their numbers are tensors).
   `attention_2`  heads, kv_heads, dim, vdim, scale, rot.{base, dims, scaling.{factor, low, high,
-                 original}} (the scaling block may be absent); causal, unit-norm queries and keys,
-                 values turned by position.  `rot.value_layout` ("halves", the default, or
+                 original}} (the scaling block may be absent); causal (or `mask.size` as above), unit-norm
+                 queries and keys, values turned by position.  `rot.value_layout` ("halves", the default, or
                  "interleaved") names how a value's elements pair up.
   `mamba2`       heads, vdim, state, groups, norm_groups, conv (taps).
 """
@@ -159,27 +159,31 @@ class VikupelConfig:
             kind = need(L, "type", where)
             m = need(L, "mixer", where)
             mw = where + "mixer."
-            if kind == "attention":
+            if kind in ("attention", "attention_2"):
+                # what the entry does not mention does not exist: no `mask` means every earlier key, no `rot` no rotation
+                window = 0
+                if m.get("mask") is not None:
+                    window = int(need(m["mask"], "size", mw + "mask."))
+                    if window <= 0:
+                        raise ConfigError(f"config.json: {mw}mask.size must be positive")
+                rot = m.get("rot")
+                if kind == "attention_2":
+                    rot = need(m, "rot", mw)
+                scaling, rot_base, rot_dims, layout = None, 0.0, 0, "halves"
+                if rot is not None:
+                    sc = rot.get("scaling")
+                    if sc:
+                        sw = mw + "rot.scaling."
+                        scaling = RopeScaling("llama3", float(need(sc, "factor", sw)), float(need(sc, "low", sw)),
+                                              float(need(sc, "high", sw)), int(need(sc, "original", sw)))
+                    rot_base, rot_dims = float(need(rot, "base", mw + "rot.")), int(need(rot, "dims", mw + "rot."))
+                    layout = str(rot.get("value_layout", "halves"))
+                second = kind == "attention_2"
                 spec = AttentionSpec(
                     heads=int(need(m, "heads", mw)), kv_heads=int(need(m, "kv_heads", mw)), dim=int(need(m, "dim", mw)),
-                    vdim=int(need(m, "vdim", mw)), scale=float(need(m, "scale", mw)),
-                    window=int(need(need(m, "mask", mw), "size", mw + "mask.")), distance_penalty=True, gate=True)
-                if spec.window <= 0:
-                    raise ConfigError(f"config.json: {mw}mask.size must be positive")
-            elif kind == "attention_2":
-                rot = need(m, "rot", mw)
-                sc = rot.get("scaling")
-                scaling = None
-                if sc:
-                    sw = mw + "rot.scaling."
-                    scaling = RopeScaling("llama3", float(need(sc, "factor", sw)), float(need(sc, "low", sw)),
-                                          float(need(sc, "high", sw)), int(need(sc, "original", sw)))
-                spec = AttentionSpec(
-                    heads=int(need(m, "heads", mw)), kv_heads=int(need(m, "kv_heads", mw)), dim=int(need(m, "dim", mw)),
-                    vdim=int(need(m, "vdim", mw)), scale=float(need(m, "scale", mw)),
-                    rot_base=float(need(rot, "base", mw + "rot.")), rot_dims=int(need(rot, "dims", mw + "rot.")),
-                    rot_scaling=scaling, unit_norm=True, rotate_values=True,
-                    value_layout=str(rot.get("value_layout", "halves")))
+                    vdim=int(need(m, "vdim", mw)), scale=float(need(m, "scale", mw)), window=window,
+                    distance_penalty=not second, gate=not second, rot_base=rot_base, rot_dims=rot_dims, rot_scaling=scaling,
+                    unit_norm=second, rotate_values=second, value_layout=layout)
             elif kind == "mamba2":
                 spec = Mamba2Spec(heads=int(need(m, "heads", mw)), vdim=int(need(m, "vdim", mw)), state=int(need(m, "state", mw)),
                                   groups=int(need(m, "groups", mw)), norm_groups=int(need(m, "norm_groups", mw)),

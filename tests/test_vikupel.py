@@ -37,7 +37,8 @@ def test_config_reads_every_size_and_constant():
 
 @pytest.mark.parametrize("edit,message", [
     (lambda d: d["layers"][0].update(type="conv"), "not a mixer"),
-    (lambda d: d["layers"][0]["mixer"].pop("mask"), "mask"),
+    (lambda d: d["layers"][0]["mixer"]["mask"].update(size=0), "mask"),
+    (lambda d: d["layers"][2]["mixer"].pop("rot"), "rot"),
     (lambda d: d["layers"][1]["mixer"].update(groups=3), "groups"),
     (lambda d: d["layers"][1]["mixer"].update(norm_groups=5), "norm_groups"),
     (lambda d: d["layers"][2]["mixer"]["rot"].update(dims=14), "rot.dims"),
@@ -53,6 +54,15 @@ def test_config_refusals(edit, message):
     edit(d)
     with pytest.raises(ConfigError, match=message):
         VikupelConfig.from_dict(d)
+
+
+def test_config_optional_window_and_rotation():
+    d = copy.deepcopy(VIKUPEL_A)
+    d["layers"][0]["mixer"].pop("mask")                       # no mask: every earlier key
+    d["layers"][2]["mixer"]["mask"] = {"size": 7}             # a window on the rotary mixer
+    c = VikupelConfig.from_dict(d)
+    assert c.layers[0].mixer.window == 0 and c.layers[0].mixer.distance_penalty
+    assert c.layers[2].mixer.window == 7 and c.layers[2].mixer.rotate_values
 
 
 def test_registry_names_and_cache_layout():

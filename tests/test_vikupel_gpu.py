@@ -99,7 +99,7 @@ def attention_reference(q, k, v, pos, H, G, scale, window, r1=None, r2=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,page,window,penalty", [(3, 1, 14, 8, 19, True), (4, 2, 64, 16, 0, False), (6, 3, 96, 16, 130, True),
+@pytest.mark.parametrize("H,G,D,page,window,penalty", [(3, 1, 14, 8, 19, True), (4, 2, 64, 16, 0, False), (6, 2, 80, 16, 130, True),
                                                          (5, 5, 40, 32, 64, False), (8, 2, 128, 16, 0, True), (2, 1, 200, 8, 257, True)])
 def test_attention_sees_exactly_its_window_and_takes_the_penalty(cuda, dtype, H, G, D, page, window, penalty):
     """The CUDA-core attention kernel on keys and values written straight into pages that lie
@@ -269,7 +269,7 @@ def test_state_space_mixer_alone(cuda, dtype, heads, P_, N, G, ng, taps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind,H,G,Dk,Dv", [("window", 3, 1, 10, 14), ("window", 6, 3, 96, 96), ("rotary", 4, 2, 64, 64), ("rotary", 2, 2, 12, 10),
+@pytest.mark.parametrize("kind,H,G,Dk,Dv", [("window", 3, 1, 10, 14), ("window", 6, 2, 80, 80), ("rotary", 4, 2, 64, 64), ("rotary", 2, 2, 12, 10),
                                             ("rotary", 4, 1, 8, 24)])
 def test_attention_mixers_alone(cuda, dtype, kind, H, G, Dk, Dv):
     from ferrum_b200.parts import RotaryEmbedding, ShapedAttention
